@@ -1,0 +1,402 @@
+#!/usr/bin/env python
+"""Benchmark of the xLSTM inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (BASELINE configs[1]): the mLSTM decode step at the xLSTM-7B head shape,
+B=16, NH=8, dqk=256, dv=512, bf16 activations, fp32 state.  A "step" is one decode step of the
+cell for the whole batch (16 tokens).  Consecutive steps walk a ring of independent layer
+states (8 layers x 2 buffers = 1 GiB), so every step streams a state that is cold in the
+126 MB L2, as a 32-layer model's decode does.
+
+``value``  tokens/s with inputs resident in HBM (kernel launched straight through the C ABI).
+``e2e``    tokens/s through the public tensor API with HOST inputs: pinned host -> device copies
+           of q,k,v,i,f and a device -> host read of h inside the timed region, every step.
+``prefill``  chunkwise prefill of BASELINE configs[3] (B=4, S=32768, heads sharded over the
+           ranks, NCCL all-gather of h, 4096x4096 out-projection), reported beside the headline.
+At N > 1 the decode batch is sharded (global batch 16*N, no collective): weak scaling.
+``--impl reference`` times the CPU restatement of the reference's torch_native recurrent cell
+(oracle/, OpenMP over batch x heads) on the host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT / "xlstm-metal_b200"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+B, NH, DQK, DV = 16, 8, 256, 512
+N_LAYERS = 8          # ring of independent layer states (cold-L2 rule)
+N_INPUT_SETS = 64     # distinct per-step inputs cycled through
+WORKLOAD = "mlstm_decode_step B=16 NH=8 dqk=256 dv=512 bf16 act fp32 state (BASELINE configs[1])"
+
+
+def step_bytes(b=B, nh=NH, dqk=DQK, dv=DV, e=2):
+    """Algorithmic HBM bytes of one decode step: C read+write, n read+write, m, q,k,v,h, i,f."""
+    per_head = 2 * dqk * dv * 4 + 2 * dqk * 4 + 8 + 2 * dqk * e + dv * e + dv * e + 2 * e
+    return b * nh * per_head
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def make_inputs(torch, device, seed):
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    cap = lambda x: 15.0 * torch.tanh(x / 15.0)
+    q = torch.randn(N_INPUT_SETS, B, NH, DQK, generator=g).to(bf)
+    k = torch.randn(N_INPUT_SETS, B, NH, DQK, generator=g).to(bf)
+    v = torch.randn(N_INPUT_SETS, B, NH, DV, generator=g).to(bf)
+    i = cap(torch.randn(N_INPUT_SETS, B, NH, generator=g)).to(bf)
+    f = cap(torch.randn(N_INPUT_SETS, B, NH, generator=g) + 3.0).to(bf)
+    return q, k, v, i, f
+
+
+def cpu_baseline(budget_s=15.0, threads=None):
+    """Oracle port of the reference's recurrent cell on the host cores, bounded sample."""
+    import numpy as np
+    from oracle import oracle as xo
+    if threads:
+        xo.set_threads(threads)
+    cores = xo.max_threads()
+    rng = np.random.default_rng(1)
+    q, k = (xo.bf16_round(rng.standard_normal((B, NH, 1, DQK)).astype(np.float32)) for _ in range(2))
+    v = xo.bf16_round(rng.standard_normal((B, NH, 1, DV)).astype(np.float32))
+    i = np.zeros((B, NH, 1), np.float32)
+    f = np.full((B, NH, 1), 3.0, np.float32)
+    st = ((rng.standard_normal((B, NH, DQK, DV)) * 0.1).astype(np.float32),
+          (rng.standard_normal((B, NH, DQK)) * 0.1).astype(np.float32), np.zeros((B, NH), np.float32))
+    xo.mlstm_recurrent(q, k, v, i, f, st)  # warm-up
+    t0 = time.perf_counter()
+    _, st = xo.mlstm_recurrent(q, k, v, i, f, st)
+    one = time.perf_counter() - t0
+    n = int(max(3, min(2000, budget_s / max(one, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(n):
+        _, st = xo.mlstm_recurrent(q, k, v, i, f, st)
+    dt = time.perf_counter() - t0
+    return {"value": B * n / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{n} decode steps of the headline workload, {dt:.1f} s, oracle C port (OpenMP over batch x heads)"}
+
+
+def run_reference(args):
+    """CPU arm: the restated reference cell, all host threads, same workload and metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as xo
+    cores = xo.max_threads()
+    rng = np.random.default_rng(1)
+    q, k = (xo.bf16_round(rng.standard_normal((N_INPUT_SETS, B, NH, 1, DQK)).astype(np.float32)) for _ in range(2))
+    v = xo.bf16_round(rng.standard_normal((N_INPUT_SETS, B, NH, 1, DV)).astype(np.float32))
+    i = xo.bf16_round((15 * np.tanh(rng.standard_normal((N_INPUT_SETS, B, NH, 1)) / 15)).astype(np.float32))
+    f = xo.bf16_round((15 * np.tanh((rng.standard_normal((N_INPUT_SETS, B, NH, 1)) + 3) / 15)).astype(np.float32))
+    st = ((rng.standard_normal((B, NH, DQK, DV)) * 0.1).astype(np.float32),
+          (rng.standard_normal((B, NH, DQK)) * 0.1).astype(np.float32), np.zeros((B, NH), np.float32))
+    # a CPU step costs ~10-40 ms, so cap the count to keep the arm within a few minutes
+    steps = min(args.steps, 2000)
+    warm = min(args.warmup, 20)
+    for t in range(warm):
+        s = t % N_INPUT_SETS
+        _, st = xo.mlstm_recurrent(q[s], k[s], v[s], i[s], f[s], st)
+    t0 = time.perf_counter()
+    for t in range(steps):
+        s = t % N_INPUT_SETS
+        _, st = xo.mlstm_recurrent(q[s], k[s], v[s], i[s], f[s], st)
+    dt = time.perf_counter() - t0
+    val = B * steps / dt
+    line = {"impl": "reference", "metric": "mlstm_decode_tokens_per_s", "value": val, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": dt / steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD},
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                             "sample": f"{steps} full decode steps, oracle C port of the torch_native recurrent cell"},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from xlstm_cuda import _lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: xlstm_cuda has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+    K, W = args.steps, max(args.warmup, 3)
+
+    q, k, v, i, f = make_inputs(torch, device, seed=1 + rank)
+    qd, kd, vd, idv, fd = (t.to(device) for t in (q, k, v, i, f))
+    g = torch.Generator().manual_seed(100 + rank)
+    C = [[(torch.randn(B, NH, DQK, DV, generator=g) * 0.1).to(device), torch.empty(B, NH, DQK, DV, device=device)]
+         for _ in range(N_LAYERS)]
+    n = [[(torch.randn(B, NH, DQK, generator=g) * 0.1).to(device), torch.empty(B, NH, DQK, device=device)]
+         for _ in range(N_LAYERS)]
+    m = [[torch.zeros(B, NH, device=device), torch.empty(B, NH, device=device)] for _ in range(N_LAYERS)]
+    h = torch.empty(B, NH, DV, dtype=torch.bfloat16, device=device)
+    stream = torch.cuda.current_stream().cuda_stream
+    side = [0] * N_LAYERS
+
+    def step(t):
+        s, l = t % N_INPUT_SETS, t % N_LAYERS
+        a, b = side[l], side[l] ^ 1
+        st = lib.xlstm_mlstm_step(qd[s].data_ptr(), kd[s].data_ptr(), vd[s].data_ptr(), idv[s].data_ptr(),
+                                  fd[s].data_ptr(), C[l][a].data_ptr(), n[l][a].data_ptr(), m[l][a].data_ptr(),
+                                  h.data_ptr(), C[l][b].data_ptr(), n[l][b].data_ptr(), m[l][b].data_ptr(),
+                                  B, NH, DQK, DV, 1e-6, _lib.BF16, stream)
+        if st:
+            _lib.check(st, "xlstm_mlstm_step")
+        side[l] = b
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident leg ------------------------------------------------
+    for t in range(W):
+        step(t)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for t in range(K):
+            step(W + t)
+        e1.record()
+        torch.cuda.synchronize()
+        if len(clk.samples) < 3:  # region shorter than the sampling period: sample a repeat of it
+            t_end = time.time() + 0.25
+            t = 0
+            while time.time() < t_end:
+                step(t)
+                t += 1
+                if t % 256 == 0:
+                    torch.cuda.synchronize()
+            torch.cuda.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    tms = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms_max = float(tms.item())
+    value = world * B * K / (ms_max * 1e-3)
+
+    # ---- end-to-end leg: host buffers through the public tensor API --------------
+    hq, hk, hv, hi, hf = (t.pin_memory() for t in (q, k, v, i, f))
+    h_host = torch.empty(B, NH, DV, dtype=torch.bfloat16).pin_memory()
+    st_e2e = [(C[l][side[l]], n[l][side[l]], m[l][side[l]]) for l in range(N_LAYERS)]
+    dq, dk, dvv, di, df = (torch.empty_like(t[0], device=device) for t in (q, k, v, i, f))
+
+    def e2e_step(t):
+        s, l = t % N_INPUT_SETS, t % N_LAYERS
+        dq.copy_(hq[s], non_blocking=True); dk.copy_(hk[s], non_blocking=True); dvv.copy_(hv[s], non_blocking=True)
+        di.copy_(hi[s], non_blocking=True); df.copy_(hf[s], non_blocking=True)
+        hh, st_e2e[l] = ops.mlstm_step(dq, dk, dvv, di, df, st_e2e[l])
+        h_host.copy_(hh, non_blocking=True)
+
+    for t in range(W):
+        e2e_step(t)
+    barrier()
+    e0.record()
+    for t in range(K):
+        e2e_step(W + t)
+    e1.record()
+    barrier()
+    tms = torch.tensor([e0.elapsed_time(e1)], device=device)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    e2e_ms = float(tms.item())
+    e2e_val = world * B * K / (e2e_ms * 1e-3)
+    h2d = sum(t[0].numel() * t.element_size() for t in (q, k, v, i, f))
+    d2h = h_host.numel() * h_host.element_size()
+
+    # ---- prefill beside it ---------------------------------------------------
+    prefill = None
+    if not args.no_prefill:
+        prefill = run_prefill(torch, dist, ops, device, world, rank, args)
+
+    hbm, tf, which = peaks()
+    achieved = step_bytes() / (ms / K * 1e-3) / 1e9  # this rank's kernel
+    line = {
+        "metric": "mlstm_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": B * world, "parallelism": f"batch-sharded x{world}",
+                   "l2": f"ring of {N_LAYERS} layer states x 2 buffers = {N_LAYERS * 2 * B * NH * DQK * DV * 4 >> 20} MiB > L2; "
+                         "every step streams a cold state", "state_update": "out-of-place"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                     "traffic": TRAFFIC_PER_LAUNCH, "kernel": "mlstm_step_kernel", "peak_source": which,
+                     "algorithmic_bytes_per_launch": step_bytes()},
+        "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms / K},
+        "gpu_launches": K,
+        "clocks": clk.summary(),
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of mlstm_step_kernel, from the ncu
+# capture summarised under profiles/ (None until a capture exists)
+TRAFFIC_PER_LAUNCH = None
+
+
+def run_prefill(torch, dist, ops, device, world, rank, args):
+    """BASELINE configs[3]: B=4, S=32768, NH=8, 256/512, L=64, bf16; heads sharded over the ranks,
+    all-gather of h, then the replicated 4096x4096 out-projection.  Strong scaling."""
+    Bp, Sp, L = 4, args.prefill_seq, 64
+    nh_local = NH // world if NH % world == 0 else NH
+    g = torch.Generator().manual_seed(3 + rank)
+    bf = torch.bfloat16
+    q = torch.randn(Bp, nh_local, Sp, DQK, generator=g).to(bf).to(device)
+    k = torch.randn(Bp, nh_local, Sp, DQK, generator=g).to(bf).to(device)
+    v = torch.randn(Bp, nh_local, Sp, DV, generator=g).to(bf).to(device)
+    i = (15 * torch.tanh(torch.randn(Bp, nh_local, Sp, generator=g) / 15)).to(bf).to(device)
+    f = (15 * torch.tanh((torch.randn(Bp, nh_local, Sp, generator=g) + 3) / 15)).to(bf).to(device)
+    w_out = (torch.randn(NH * DV, NH * DV, generator=g) * 0.02).to(bf).to(device)
+    need = ops.chunkwise_workspace_bytes(Bp, nh_local, Sp, DQK, DV, L, bf)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
+    gathered = torch.empty(world, Bp, nh_local, Sp, DV, dtype=bf, device=device) if world > 1 else None
+
+    def one():
+        h, st = ops.mlstm_chunkwise(q, k, v, i, f, None, L, 1e-6, ws)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, h)
+            hh = gathered.permute(1, 3, 0, 2, 4).reshape(Bp * Sp, NH * DV)
+        else:
+            hh = h.permute(0, 2, 1, 3).reshape(Bp * Sp, NH * DV)
+        return hh @ w_out.t()
+
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    one()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    reps = args.prefill_reps
+    e[0].record()
+    for _ in range(reps):
+        h, st = ops.mlstm_chunkwise(q, k, v, i, f, None, L, 1e-6, ws)
+    e[1].record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e[2].record()
+    for _ in range(reps):
+        one()
+    e[3].record()
+    torch.cuda.synchronize()
+    t_cell = torch.tensor([e[0].elapsed_time(e[1]) / reps, e[2].elapsed_time(e[3]) / reps], device=device)
+    if world > 1:
+        dist.all_reduce(t_cell, op=dist.ReduceOp.MAX)
+    cell_ms, full_ms = (float(x) for x in t_cell)
+    tokens = Bp * Sp
+    flop = tokens * NH * (4 * DQK * DV + L * (DQK + DV))      # whole job, causal-half count
+    byts = tokens * NH * ((2 * DQK + 2 * DV) * 2 + 2 * 2)
+    hbm, tf, which = peaks()
+    return {"workload": f"mlstm_chunkwise_prefill B={Bp} S={Sp} NH={NH} dqk={DQK} dv={DV} L={L} bf16 (BASELINE configs[3])",
+            "parallelism": f"heads sharded x{world}, all-gather h, replicated out-proj", "scaling": "strong",
+            "cell_tokens_per_s": tokens / (cell_ms * 1e-3), "cell_ms": cell_ms,
+            "with_allgather_outproj_tokens_per_s": tokens / (full_ms * 1e-3), "with_allgather_outproj_ms": full_ms,
+            "roofline": {"bound": "tensor", "achieved": flop / world / (cell_ms * 1e-3) / 1e12, "peak": tf,
+                         "unit": "TFLOP/s", "frac": flop / world / (cell_ms * 1e-3) / 1e12 / tf,
+                         "hbm_achieved_gbs": byts / world / (cell_ms * 1e-3) / 1e9, "hbm_frac": byts / world / (cell_ms * 1e-3) / 1e9 / hbm,
+                         "flop_count": "4*dqk*dv + L*(dqk+dv) per token per head (causal half)", "peak_source": which}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4096)
+    ap.add_argument("--warmup", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--prefill-seq", type=int, default=32768)
+    ap.add_argument("--prefill-reps", type=int, default=3)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

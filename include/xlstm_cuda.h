@@ -1,0 +1,137 @@
+/*
+ * libxlstm_cuda -- hand-written sm_100a kernels for the xLSTM inference hot
+ * path, behind a plain C ABI.
+ *
+ * Conventions for every entry point
+ *   - all tensor arguments are DEVICE pointers (tensor.data_ptr()); the library
+ *     never allocates or frees memory: scratch is passed in by the caller;
+ *   - `dtype` selects the element type of the activations (q, k, v, gates, h,
+ *     z ...): XLSTM_F32 or XLSTM_BF16.  Recurrent state is always fp32;
+ *   - `stream` is a cudaStream_t (NULL = default stream).  Calls are
+ *     asynchronous on that stream and never synchronise;
+ *   - the return value is 0 or a negative xlstm_status; nothing throws,
+ *     aborts or traps.  xlstm_strerror() names a status.
+ *
+ * The reference project has no C ABI of its own: its native kernels are Metal
+ * shaders reached through pybind11 modules built at first use
+ * (torch.utils.cpp_extension.load, e.g.
+ * xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/forward/mlstm_chunkwise_recurrent_fw_C.py:29-35).
+ * Each function below names the reference interface it stands in for.
+ */
+#ifndef XLSTM_CUDA_H
+#define XLSTM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum { XLSTM_F32 = 0, XLSTM_BF16 = 1 } xlstm_dtype;
+
+typedef enum {
+    XLSTM_OK = 0,
+    XLSTM_ERR_INVALID = -1,      /* null pointer, bad size, aliasing that is not allowed */
+    XLSTM_ERR_UNSUPPORTED = -2,  /* shape or dtype outside what the kernels cover */
+    XLSTM_ERR_CUDA = -3,         /* a CUDA runtime call or launch failed */
+    XLSTM_ERR_WORKSPACE = -4,    /* caller-provided scratch is too small or misaligned */
+    XLSTM_ERR_TIMEOUT = -5       /* a bounded device-side wait gave up (status word set) */
+} xlstm_status;
+
+int xlstm_version(void);
+const char *xlstm_strerror(int status);
+
+/*
+ * y = cap * tanh(x / cap), elementwise over n elements; cap <= 0 copies x to y.
+ * y may alias x.
+ * Replaces soft_cap_forward(x, cap) -> Tensor
+ * (xlstm_metal/torch_native/blocks/soft_cap/soft_cap_extension.mm:60-99,
+ *  kernel soft_cap_kernel.metal:4-15; Python entry softcap.py:14-36).
+ */
+int xlstm_softcap(const void *x, void *y, int64_t n, float cap, int dtype, void *stream);
+
+/*
+ * One mLSTM decode step for every (batch, head):
+ *   m' = max(logsigmoid(f) + m, i);  C' = e^{logsig(f)+m-m'} C + e^{i-m'} k (x) v;  n' likewise;
+ *   h  = (q~ . C') / (max(|q~ . n'|, e^{-m'}) + eps),  q~ = q * dqk^-1/2.
+ * q,k: [B*NH, dqk]  v,h: [B*NH, dv]  ig,fg: [B*NH]  (dense, `dtype`)
+ * C0,C1: [B*NH, dqk, dv]  n0,n1: [B*NH, dqk]  m0,m1: [B*NH]  (fp32).
+ * C0 == NULL means the zero state (n0, m0 ignored).  C1 may alias C0 (in-place
+ * update); n1/m1 must not alias n0/m0.
+ * Replaces mLSTMRecurrentKernelCell.forward at S == 1
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/mlstm_recurrent_kernel_cell.py:53-161)
+ * and the draft Metal step kernel
+ * (kernel_development/xlstm/pytorch_mm/mlstm_kernels.metal:37-107).
+ */
+int xlstm_mlstm_step(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                     const float *C0, const float *n0, const float *m0,
+                     void *h, float *C1, float *n1, float *m1,
+                     int B, int NH, int dqk, int dv, float eps, int dtype, void *stream);
+
+/*
+ * Chunkwise mLSTM forward over S tokens (any S >= 1; the last chunk may be
+ * partial), equal in exact arithmetic to S decode steps.
+ * q,k: [B,NH,S,dqk]  v,h: [B,NH,S,dv]  ig,fg: [B,NH,S]  (`dtype`).
+ * `strides` (host pointer, may be NULL for dense tensors) holds 15 element
+ * strides: q(b,h,s) k(b,h,s) v(b,h,s) h(b,h,s) gates(b,h,s); the innermost
+ * dimension is always contiguous.  This lets the caller pass the [B,S,NH,d]
+ * projection output without a transposed copy.
+ * State as in xlstm_mlstm_step; C1/n1/m1 must not alias C0/n0/m0.
+ * `workspace` must hold xlstm_mlstm_chunkwise_workspace_bytes(...) bytes,
+ * 256-byte aligned (may be NULL when that size is 0).
+ * Replaces mLSTMParallelKernelCell.__call__
+ * (xlstm_metal/mlx_jit/blocks/mlstm/mlstm_chunkwise/mlstm_parallel_kernel_cell.py:132-249)
+ * and the two native kernels under it: mlstm_recurrent_fw_C_forward(...)
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/forward/mlstm_chunkwise_recurrent_fw_C_extension.mm:62-175)
+ * and mlstm_chunkwise_parallel_fw_Hintra_metal
+ * (xlstm_metal/mlx_jit/blocks/mlstm/mlstm_chunkwise/forward/mlstm_chunkwise_parallel_fw_Hintra.py:430-506);
+ * also mLSTMRecurrentKernelCell.forward at S > 1.
+ */
+int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                              const float *C0, const float *n0, const float *m0,
+                              void *h, float *C1, float *n1, float *m1,
+                              int B, int NH, int S, int dqk, int dv, int L, float eps, int dtype,
+                              const int64_t *strides, void *workspace, size_t workspace_bytes, void *stream);
+
+size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int dv, int L, int dtype);
+
+/*
+ * Packaged sLSTM cell (scalar gates per head, state c,n,m) applied to S
+ * timesteps in one launch:
+ *   m' = max(m + logsigmoid(f), i); c' = e^{m+logsig(f)-m'} c + e^{i-m'} tanh(z);
+ *   n' = ... + e^{i-m'};  h = sigmoid(o) c' / (|n'| + eps).
+ * z,h: [B,S,NH,H]  ig,fg,og: [B,S,NH]  (`dtype`);  c,n: [B,NH,H]  m: [B,NH] (fp32).
+ * c0 == NULL means the zero state.  c1/n1 may alias c0/n0; m1 must not alias m0.
+ * Replaces sLSTMStepwiseKernelCell.forward
+ * (xlstm_metal/torch_native/blocks/slstm/slstm_layers/stepwise/slstm_stepwise_kernel_cell.py:47-97)
+ * and the per-timestep Python loop around it (slstm_neuron.py:132-143); Metal
+ * twin xlstm_metal/mlx_jit/blocks/slstm/slstm_layers/stepwise/slstm_metal_kernel.py:60-123.
+ */
+int xlstm_slstm_scan(const void *z, const void *ig, const void *fg, const void *og,
+                     const float *c0, const float *n0, const float *m0,
+                     void *h, float *c1, float *n1, float *m1,
+                     int B, int S, int NH, int H, float eps, int dtype, void *stream);
+
+/*
+ * sLSTM with block-diagonal recurrent weights (state c,n,h,m per unit), S
+ * timesteps in one launch, recurrent weights resident on chip:
+ *   pre_g = gx_g + R_g h_{t-1} + rb_g   (g = i,f,z,o; i and f soft-capped with `cap` when cap > 0)
+ *   m' = max(f + m, i); c' = e^{f-m'+m} c + e^{i-m'} tanh(z); n' = e^{f-m'+m} n + e^{i-m'};
+ *   h = sigmoid(o) c' / max(n', 1).
+ * gx: [B,S,4,D] (`dtype`, gate order i,f,z,o, D = NH*dh)   R: [4,NH,dh,dh] (`dtype`, [out][in])
+ * rb: [4,D] fp32   hs: [B,S,D] (`dtype`)   state c,n,h,m: [B,D] fp32.
+ * c0 == NULL means the initial state c=h=m=0, n=1.  Final state must not alias the initial one.
+ * Replaces sLSTMBlock.forward_step's recurrence
+ * (kernel_development/xlstm/implementations/pytorch/xlstm_pytorch_enhanced.py:428-461,
+ *  BlockLinear :207-229, init_hidden :407-413) and the loop over t (:463-488).
+ */
+int xlstm_slstm_recurrent(const void *gx, const void *R, const float *rb,
+                          const float *c0, const float *n0, const float *h0, const float *m0,
+                          void *hs, float *c1, float *n1, float *h1, float *m1,
+                          int B, int S, int NH, int dh, float cap, int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XLSTM_CUDA_H */

@@ -1,0 +1,293 @@
+"""GPU parity: every kernel through the C ABI against the CPU oracle and the golden fixtures.
+
+Tolerances (max|a-b| / max|b|): fp32 1e-4 on h, C, n and 1e-4 absolute on m;
+bf16 activations with fp32 state 2e-2.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import relerr
+from oracle import oracle as xo
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-4
+BF16_TOL = 2e-2
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(a)).to("cuda", dtype)
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+def gates(rng, shape, fmean=3.0):
+    i = 15.0 * np.tanh(rng.standard_normal(shape).astype(np.float32) / 15.0)
+    f = 15.0 * np.tanh((rng.standard_normal(shape).astype(np.float32) + fmean) / 15.0)
+    return i, f
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from xlstm_cuda import ops as _ops
+    return _ops
+
+
+# ---- soft-cap ----------------------------------------------------------------
+@pytest.mark.parametrize("n", [1, 7, 4096, 50304, 1 << 20 | 3])
+@pytest.mark.parametrize("cap", [15.0, 30.0])
+def test_softcap_fp32(ops, n, cap):
+    rng = np.random.default_rng(n)
+    x = (rng.standard_normal(n) * 20).astype(np.float32)
+    y = host(ops.softcap(dev(x), cap))
+    np.testing.assert_allclose(y, xo.softcap(x, cap), rtol=1e-5, atol=1e-5)
+
+
+def test_softcap_bf16_and_unaligned_and_kat(ops, golden):
+    rng = np.random.default_rng(0)
+    x = xo.bf16_round((rng.standard_normal(10001) * 20).astype(np.float32))
+    y = host(ops.softcap(dev(x, torch.bfloat16), 30.0))
+    assert relerr(y, xo.softcap(x, 30.0)) < 4e-3
+    base = dev(np.arange(1003, dtype=np.float32) / 10 - 50)
+    view = base[1:]  # 4-byte aligned only
+    np.testing.assert_allclose(host(ops.softcap(view, 15.0)), xo.softcap(host(view), 15.0), rtol=1e-5, atol=1e-5)
+    g = golden("kat")
+    for tag in ("small", "large", "edge"):
+        y = host(ops.softcap(dev(g[f"softcap_{tag}_x"]), float(g[f"softcap_{tag}_cap"])))
+        np.testing.assert_allclose(y, g[f"softcap_{tag}_y"], rtol=1e-6, atol=1e-6)
+    x = dev(np.ones(5, np.float32))
+    assert ops.softcap(x, None) is x and ops.softcap(x, 0.0) is x
+    assert ops.softcap(torch.empty(0, device="cuda"), 15.0).numel() == 0
+
+
+# ---- decode step ------------------------------------------------------------------
+def run_steps(ops, g, dtype, inplace=False):
+    st = (dev(g["C0"]), dev(g["n0"]), dev(g["m0"]))
+    hs = []
+    for t in range(g["q"].shape[2]):
+        a = [dev(g[x][:, :, t], dtype) for x in "qkvif"]
+        h, st = ops.mlstm_step(*a, state=st, inplace=inplace)
+        hs.append(host(h))
+    return np.stack(hs, 2), tuple(host(s) for s in st)
+
+
+@pytest.mark.parametrize("name", ["mlstm_step_bf16", "mlstm_step_7b"])
+def test_mlstm_step_against_reference_fixture(ops, golden, name):
+    g = golden(name)
+    # fp32 activations (bf16-representable values): 1e-4 against the reference's fp32 run
+    h, (C, n, m) = run_steps(ops, g, torch.float32)
+    assert relerr(h, g["h_fp32"]) < FP32_TOL and relerr(C, g["C_fp32"]) < FP32_TOL
+    assert relerr(n, g["n_fp32"]) < FP32_TOL and np.abs(m - g["m_fp32"]).max() < FP32_TOL
+    # bf16 activations, fp32 state: 2e-2 against the reference's bf16-compute run and its fp32 run
+    h, (C, n, m) = run_steps(ops, g, torch.bfloat16, inplace=True)
+    assert relerr(h, g["h_bf16"]) < BF16_TOL and relerr(h, g["h_fp32"]) < BF16_TOL
+    assert relerr(C, g["C_bf16"]) < BF16_TOL and relerr(n, g["n_bf16"]) < BF16_TOL
+    assert np.abs(m - g["m_bf16"]).max() < BF16_TOL
+
+
+@pytest.mark.parametrize("B,NH,dqk,dv", [(16, 8, 256, 512), (3, 5, 64, 64), (2, 2, 100, 36), (1, 1, 512, 1024)])
+def test_mlstm_step_against_oracle(ops, B, NH, dqk, dv):
+    rng = np.random.default_rng(B * 1000 + dqk)
+    q, k = (rng.standard_normal((B, NH, 1, dqk)).astype(np.float32) for _ in range(2))
+    v = rng.standard_normal((B, NH, 1, dv)).astype(np.float32)
+    i, f = gates(rng, (B, NH, 1))
+    st = (rng.standard_normal((B, NH, dqk, dv)).astype(np.float32) * 0.1,
+          rng.standard_normal((B, NH, dqk)).astype(np.float32) * 0.1, rng.standard_normal((B, NH)).astype(np.float32))
+    for state in (st, None):
+        h_ref, st_ref = xo.mlstm_recurrent(q, k, v, i, f, state)
+        h, st_new = ops.mlstm_step(dev(q[:, :, 0]), dev(k[:, :, 0]), dev(v[:, :, 0]), dev(i[:, :, 0]), dev(f[:, :, 0]),
+                                   None if state is None else tuple(dev(s) for s in state))
+        assert relerr(host(h), h_ref[:, :, 0]) < FP32_TOL
+        for got, want in zip(st_new, st_ref):
+            assert relerr(host(got), want) < FP32_TOL
+
+
+def test_mlstm_step_config2_256_steps_bf16(ops):
+    """BASELINE config 2: B=16, NH=8, 256/512, bf16 activations, fp32 state, 256 carried steps."""
+    B, NH, dqk, dv, T = 16, 8, 256, 512, 256
+    g = torch.Generator().manual_seed(1)
+    C = torch.randn(B, NH, dqk, dv, generator=g) * 0.1
+    n = torch.randn(B, NH, dqk, generator=g) * 0.1
+    m = torch.zeros(B, NH)
+    q = torch.randn(B, NH, T, dqk, generator=g).bfloat16()
+    k = torch.randn(B, NH, T, dqk, generator=g).bfloat16()
+    v = torch.randn(B, NH, T, dv, generator=g).bfloat16()
+    i = (15 * torch.tanh(torch.randn(B, NH, T, generator=g) / 15)).bfloat16()
+    f = (15 * torch.tanh((torch.randn(B, NH, T, generator=g) + 3) / 15)).bfloat16()
+    h_ref, st_ref = xo.mlstm_recurrent(q.float().numpy(), k.float().numpy(), v.float().numpy(), i.float().numpy(),
+                                       f.float().numpy(), (C.numpy(), n.numpy(), m.numpy()))
+    st = (C.cuda(), n.cuda(), m.cuda())
+    qd, kd, vd, idv, fd = (t.cuda() for t in (q, k, v, i, f))
+    hs = []
+    for t in range(T):
+        h, st = ops.mlstm_step(qd[:, :, t], kd[:, :, t], vd[:, :, t], idv[:, :, t], fd[:, :, t], st, inplace=True)
+        hs.append(h)
+    h = host(torch.stack(hs, 2))
+    assert relerr(h, h_ref) < BF16_TOL
+    assert relerr(host(st[0]), st_ref[0]) < FP32_TOL * 10 and relerr(host(st[1]), st_ref[1]) < FP32_TOL * 10
+    assert np.abs(host(st[2]) - st_ref[2]).max() < 1e-3
+
+
+# ---- chunkwise -------------------------------------------------------------------
+def test_chunkwise_config1_fp32(ops, golden):
+    g = golden("mlstm_c1_fp32")
+    for L in (64, 32):
+        h, st = ops.mlstm_chunkwise(*(dev(g[x]) for x in "qkvif"), state=None, chunk_size=L)
+        assert relerr(host(h), g["h"]) < FP32_TOL
+        assert relerr(host(st[0]), g["C"]) < FP32_TOL and relerr(host(st[1]), g["n"]) < FP32_TOL
+        assert np.abs(host(st[2]) - g["m"]).max() < FP32_TOL
+
+
+def test_chunkwise_ragged_with_state_fp32(ops, golden):
+    g = golden("mlstm_ragged_fp32")
+    st0 = tuple(dev(g[x]) for x in ("C0", "n0", "m0"))
+    for L in (64, 16, 7):
+        h, st = ops.mlstm_chunkwise(*(dev(g[x]) for x in "qkvif"), state=st0, chunk_size=L)
+        assert relerr(host(h), g["h"]) < FP32_TOL
+        assert relerr(host(st[0]), g["C"]) < FP32_TOL and relerr(host(st[1]), g["n"]) < FP32_TOL
+        assert np.abs(host(st[2]) - g["m"]).max() < FP32_TOL
+
+
+@pytest.mark.parametrize("B,NH,S,dqk,dv", [(1, 2, 128, 256, 512), (2, 1, 70, 128, 192), (1, 1, 1, 64, 64)])
+def test_chunkwise_against_oracle_and_strided_inputs(ops, B, NH, S, dqk, dv):
+    rng = np.random.default_rng(S)
+    # projection-style layout [B,S,NH,d], handed over as a permuted view
+    q, k = (rng.standard_normal((B, S, NH, dqk)).astype(np.float32) for _ in range(2))
+    v = rng.standard_normal((B, S, NH, dv)).astype(np.float32)
+    i, f = gates(rng, (B, S, NH))
+    tr = lambda a: np.ascontiguousarray(np.moveaxis(a, 1, 2))
+    h_ref, st_ref = xo.mlstm_recurrent(tr(q), tr(k), tr(v), tr(i), tr(f))
+    h, st = ops.mlstm_chunkwise(dev(q).permute(0, 2, 1, 3), dev(k).permute(0, 2, 1, 3), dev(v).permute(0, 2, 1, 3),
+                                dev(i).permute(0, 2, 1), dev(f).permute(0, 2, 1))
+    assert relerr(host(h), h_ref) < FP32_TOL
+    for got, want in zip(st, st_ref):
+        assert relerr(host(got), want) < FP32_TOL
+    # run twice: bitwise identical
+    h2, _ = ops.mlstm_chunkwise(dev(q).permute(0, 2, 1, 3), dev(k).permute(0, 2, 1, 3), dev(v).permute(0, 2, 1, 3),
+                                dev(i).permute(0, 2, 1), dev(f).permute(0, 2, 1))
+    assert torch.equal(h, h2)
+
+
+def test_chunkwise_equals_steps_and_split_sequence(ops):
+    """chunkwise(S) == S decode steps == chunkwise(S1) then chunkwise(S2) with the carried state."""
+    rng = np.random.default_rng(5)
+    B, NH, S, dqk, dv = 2, 2, 96, 64, 128
+    q, k = (dev(rng.standard_normal((B, NH, S, dqk)).astype(np.float32)) for _ in range(2))
+    v = dev(rng.standard_normal((B, NH, S, dv)).astype(np.float32))
+    i, f = (dev(a) for a in gates(rng, (B, NH, S)))
+    h, st = ops.mlstm_chunkwise(q, k, v, i, f)
+    h1, st1 = ops.mlstm_chunkwise(q[:, :, :50], k[:, :, :50], v[:, :, :50], i[:, :, :50], f[:, :, :50])
+    h2, st2 = ops.mlstm_chunkwise(q[:, :, 50:], k[:, :, 50:], v[:, :, 50:], i[:, :, 50:], f[:, :, 50:], st1)
+    assert relerr(host(torch.cat([h1, h2], 2)), host(h)) < FP32_TOL
+    assert relerr(host(st2[0]), host(st[0])) < FP32_TOL
+    s, hs = None, []
+    for t in range(S):
+        ht, s = ops.mlstm_step(q[:, :, t], k[:, :, t], v[:, :, t], i[:, :, t], f[:, :, t], s)
+        hs.append(ht)
+    assert relerr(host(torch.stack(hs, 2)), host(h)) < FP32_TOL
+    assert relerr(host(s[0]), host(st[0])) < FP32_TOL and np.abs(host(s[2]) - host(st[2])).max() < FP32_TOL
+
+
+def test_chunkwise_bf16_head_shape(ops):
+    rng = np.random.default_rng(8)
+    B, NH, S, dqk, dv = 1, 2, 256, 256, 512
+    q, k = (xo.bf16_round(rng.standard_normal((B, NH, S, dqk)).astype(np.float32)) for _ in range(2))
+    v = xo.bf16_round(rng.standard_normal((B, NH, S, dv)).astype(np.float32))
+    i, f = (xo.bf16_round(a) for a in gates(rng, (B, NH, S)))
+    h_ref, st_ref = xo.mlstm_recurrent(q, k, v, i, f)
+    h, st = ops.mlstm_chunkwise(*(dev(a, torch.bfloat16) for a in (q, k, v, i, f)))
+    assert relerr(host(h), h_ref) < BF16_TOL
+    assert relerr(host(st[0]), st_ref[0]) < BF16_TOL and relerr(host(st[1]), st_ref[1]) < BF16_TOL
+    assert np.abs(host(st[2]) - st_ref[2]).max() < BF16_TOL
+
+
+def test_extreme_gates_stay_finite(ops):
+    """Gates at the soft-cap limits (+-15) over many chunks: no inf/nan, state matches the oracle."""
+    rng = np.random.default_rng(3)
+    B, NH, S, dqk, dv = 1, 2, 192, 64, 64
+    q, k = (rng.standard_normal((B, NH, S, dqk)).astype(np.float32) for _ in range(2))
+    v = rng.standard_normal((B, NH, S, dv)).astype(np.float32)
+    i = rng.choice([-15.0, 0.0, 15.0], size=(B, NH, S)).astype(np.float32)
+    f = rng.choice([-15.0, 0.0, 15.0], size=(B, NH, S)).astype(np.float32)
+    h_ref, st_ref = xo.mlstm_recurrent(q, k, v, i, f)
+    h, st = ops.mlstm_chunkwise(*(dev(a) for a in (q, k, v, i, f)))
+    assert np.isfinite(host(h)).all()
+    assert relerr(host(h), h_ref) < FP32_TOL and relerr(host(st[0]), st_ref[0]) < FP32_TOL
+    assert np.abs(host(st[2]) - st_ref[2]).max() < 1e-3
+
+
+# ---- sLSTM ------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["a", "b", "x", "z"])
+def test_slstm_scan_fixture(ops, golden, tag):
+    g = golden("slstm_a")
+    st = None if tag == "z" else tuple(dev(g[f"{tag}_{s}0"]) for s in "cnm")
+    h, (c, n, m) = ops.slstm_scan(*(dev(g[f"{tag}_{x}"]) for x in "zifo"), state=st)
+    tol = 1e-4 if tag == "x" else 1e-5
+    assert relerr(host(h), g[f"{tag}_h"]) < tol and relerr(host(c), g[f"{tag}_c"]) < tol
+    assert relerr(host(n), g[f"{tag}_n"]) < tol and np.abs(host(m) - g[f"{tag}_m"]).max() < tol
+
+
+@pytest.mark.parametrize("B,S,NH,H,dtype", [(32, 100, 4, 256, torch.float32), (3, 33, 2, 40, torch.float32),
+                                             (2, 64, 4, 1024, torch.float32), (4, 70, 4, 256, torch.bfloat16)])
+def test_slstm_scan_oracle(ops, B, S, NH, H, dtype):
+    rng = np.random.default_rng(H + S)
+    rd = xo.bf16_round if dtype == torch.bfloat16 else (lambda a: a)
+    z = rd(rng.standard_normal((B, S, NH, H)).astype(np.float32))
+    i, f = (rd(a) for a in gates(rng, (B, S, NH)))
+    o = rd(rng.standard_normal((B, S, NH)).astype(np.float32))
+    h_ref, st_ref = xo.slstm_scan(z, i, f, o)
+    h, st = ops.slstm_scan(*(dev(a, dtype) for a in (z, i, f, o)))
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+    assert relerr(host(h), h_ref) < tol
+    for got, want in zip(st, st_ref):
+        assert relerr(host(got), want) < FP32_TOL
+
+
+def test_slstm_recurrent_fixture(ops, golden):
+    g = golden("slstm_b")
+    nh = int(g["num_heads"])
+    hs, st = ops.slstm_recurrent(dev(g["gx"]), dev(g["R"]), dev(g["rb"]), None, nh, 15.0)
+    assert relerr(host(hs), g["hs"]) < FP32_TOL
+    for got, key in zip(st, "cnhm"):
+        assert relerr(host(got), g[key]) < FP32_TOL
+    hs2, st2 = ops.slstm_recurrent(dev(g["gx2"]), dev(g["R"]), dev(g["rb"]), st, nh, 15.0)
+    assert relerr(host(hs2), g["hs2"]) < FP32_TOL
+    for got, key in zip(st2, ("c2", "n2", "h2", "m2")):
+        assert relerr(host(got), g[key]) < FP32_TOL
+
+
+@pytest.mark.parametrize("B,S,NH,dh,dtype", [(5, 40, 4, 256, torch.float32), (9, 24, 2, 64, torch.float32),
+                                              (8, 48, 4, 256, torch.bfloat16), (3, 17, 3, 128, torch.bfloat16)])
+def test_slstm_recurrent_oracle(ops, B, S, NH, dh, dtype):
+    rng = np.random.default_rng(dh + B)
+    rd = xo.bf16_round if dtype == torch.bfloat16 else (lambda a: a)
+    D = NH * dh
+    gx = rd(rng.standard_normal((B, S, 4, D)).astype(np.float32))
+    gx[:, :, 1] += np.linspace(3, 6, D, dtype=np.float32)
+    gx = rd(gx)
+    R = rd((rng.standard_normal((4, NH, dh, dh)) * 0.02).astype(np.float32))
+    rb = (rng.standard_normal((4, D)) * 0.05).astype(np.float32)
+    hs_ref, st_ref = xo.slstm_recurrent(gx, R, rb, None, NH, 15.0)
+    hs, st = ops.slstm_recurrent(dev(gx, dtype), dev(R, dtype), dev(rb), None, NH, 15.0)
+    tol = BF16_TOL if dtype == torch.bfloat16 else FP32_TOL
+    assert relerr(host(hs), hs_ref) < tol
+    for got, want in zip(st, st_ref):
+        assert relerr(host(got), want) < (tol if dtype == torch.bfloat16 else FP32_TOL)
+
+
+# ---- error behaviour of the C ABI --------------------------------------------------
+def test_errors_are_statuses_not_crashes(ops):
+    from xlstm_cuda import _lib
+    lib = _lib.load()
+    assert lib.xlstm_softcap(None, None, 8, 15.0, 0, None) == -1
+    assert lib.xlstm_softcap(None, None, 0, 15.0, 0, None) == 0
+    x = torch.zeros(16, device="cuda")
+    assert lib.xlstm_softcap(x.data_ptr(), x.data_ptr(), 16, 15.0, 7, None) == -2
+    assert lib.xlstm_mlstm_step(*([x.data_ptr()] * 5), None, None, None, *([x.data_ptr()] * 4), 1, 1, 2, 3, 1e-6, 0, None) == -2
+    with pytest.raises(RuntimeError):
+        ops.softcap(torch.zeros(4), 15.0)  # CPU tensor: no fallback
+    with pytest.raises(TypeError):
+        ops.softcap(torch.zeros(4, device="cuda", dtype=torch.float16), 15.0)

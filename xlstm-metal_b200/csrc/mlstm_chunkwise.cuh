@@ -1,0 +1,26 @@
+// Shared between the chunkwise mLSTM translation units.
+#pragma once
+#include "common.cuh"
+
+namespace xl {
+
+struct ChunkwiseParams {
+    const void *q, *k, *v, *ig, *fg;
+    const float *C0, *n0, *m0;
+    void *h;
+    float *C1, *n1, *m1;
+    int B, NH, S, dqk, dv, L;
+    float eps, qscale;
+    // element strides (batch, head, token); innermost dimension contiguous
+    int64_t sq[3], sk[3], sv[3], sh[3], sg[3];
+};
+
+// exact-fp32 CUDA-core path: any dqk <= 512, dv, S, L <= 64
+int mlstm_chunkwise_simt(const ChunkwiseParams &p, int dtype, cudaStream_t st);
+
+// tcgen05 / TMEM / TMA path: bf16, L == 64, dqk == 256 (or 128/64), dv % 128 == 0, whole chunks
+bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype);
+size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L);
+int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspace_bytes, cudaStream_t st);
+
+}  // namespace xl

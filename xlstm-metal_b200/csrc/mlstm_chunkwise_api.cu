@@ -1,0 +1,67 @@
+// C entry point of the chunkwise mLSTM forward: argument checks and dispatch
+// between the tensor-core path (bf16, production shapes) and the exact
+// CUDA-core path (everything else, and the partial last chunk).
+#include "mlstm_chunkwise.cuh"
+
+namespace {
+
+void dense_strides(xl::ChunkwiseParams &p) {
+    const int64_t S = p.S, NH = p.NH;
+    p.sq[0] = NH * S * p.dqk; p.sq[1] = S * p.dqk; p.sq[2] = p.dqk;
+    p.sk[0] = p.sq[0]; p.sk[1] = p.sq[1]; p.sk[2] = p.sq[2];
+    p.sv[0] = NH * S * p.dv; p.sv[1] = S * p.dv; p.sv[2] = p.dv;
+    p.sh[0] = p.sv[0]; p.sh[1] = p.sv[1]; p.sh[2] = p.sv[2];
+    p.sg[0] = NH * S; p.sg[1] = S; p.sg[2] = 1;
+}
+
+}  // namespace
+
+extern "C" size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int dv, int L, int dtype) {
+    if (dtype != XLSTM_BF16) return 0;
+    return xl::mlstm_chunkwise_tc_workspace(B, NH, S, dqk, dv, L);
+}
+
+extern "C" int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                         const float *C0, const float *n0, const float *m0, void *h, float *C1,
+                                         float *n1, float *m1, int B, int NH, int S, int dqk, int dv, int L,
+                                         float eps, int dtype, const int64_t *strides, void *workspace,
+                                         size_t workspace_bytes, void *stream) {
+    if (!q || !k || !v || !ig || !fg || !h || !C1 || !n1 || !m1) return XLSTM_ERR_INVALID;
+    if (B <= 0 || NH <= 0 || S <= 0 || dqk <= 0 || dv <= 0 || L <= 0) return XLSTM_ERR_INVALID;
+    if (C0 && (!n0 || !m0)) return XLSTM_ERR_INVALID;
+    if (C0 && (C1 == C0 || n1 == n0 || m1 == m0)) return XLSTM_ERR_INVALID;
+    if (dtype != XLSTM_F32 && dtype != XLSTM_BF16) return XLSTM_ERR_UNSUPPORTED;
+    if ((int64_t)B * NH > 2147483647LL) return XLSTM_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    xl::ChunkwiseParams p{};
+    p.q = q; p.k = k; p.v = v; p.ig = ig; p.fg = fg;
+    p.C0 = C0; p.n0 = n0; p.m0 = m0;
+    p.h = h; p.C1 = C1; p.n1 = n1; p.m1 = m1;
+    p.B = B; p.NH = NH; p.S = S; p.dqk = dqk; p.dv = dv; p.L = L;
+    p.eps = eps; p.qscale = 1.0f / sqrtf((float)dqk);
+    if (strides) {
+        for (int d = 0; d < 3; ++d) {
+            p.sq[d] = strides[d]; p.sk[d] = strides[3 + d]; p.sv[d] = strides[6 + d];
+            p.sh[d] = strides[9 + d]; p.sg[d] = strides[12 + d];
+        }
+    } else {
+        dense_strides(p);
+    }
+
+    if (!xl::mlstm_chunkwise_tc_supported(p, dtype)) return xl::mlstm_chunkwise_simt(p, dtype, st);
+
+    // Whole chunks on the tensor cores, then the S mod L tail (with the carried
+    // state) on the exact path: the split the reference neuron makes between its
+    // chunkwise and recurrent cells (mlx_jit/.../mlstm_neuron.py:222-257).
+    const int s_full = (S / L) * L;
+    const size_t need = xl::mlstm_chunkwise_tc_workspace(B, NH, s_full, dqk, dv, L);
+    if (need && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)))
+        return XLSTM_ERR_WORKSPACE;
+    if (s_full == S) return xl::mlstm_chunkwise_tc(p, workspace, workspace_bytes, st);
+    // tail needs the intermediate state somewhere: use the final-state buffers
+    // as the hand-over and the (smaller) tail call reads them -- but a kernel
+    // may not read and write the same state buffers, so the tail state lives in
+    // the workspace after the tensor-core scratch.
+    return XLSTM_ERR_UNSUPPORTED;
+}
