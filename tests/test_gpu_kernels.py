@@ -204,8 +204,28 @@ def test_chunkwise_bf16_head_shape(ops):
     assert np.abs(host(st[2]) - st_ref[2]).max() < BF16_TOL
 
 
+def recurrent_fp64(q, k, v, i, f, eps=1e-6):
+    """The recurrence in float64 (numpy), for inputs where fp32 itself is the limit."""
+    q, k, v, i, f = (a.astype(np.float64) for a in (q, k, v, i, f))
+    B, NH, S, dqk = q.shape
+    C = np.zeros((B, NH, dqk, v.shape[-1])); n = np.zeros((B, NH, dqk)); m = np.zeros((B, NH)); hs = []
+    for t in range(S):
+        fl = -np.logaddexp(0, -f[:, :, t])
+        mn = np.maximum(fl + m, i[:, :, t])
+        fg, ig = np.exp(fl + m - mn), np.exp(i[:, :, t] - mn)
+        C = fg[..., None, None] * C + ig[..., None, None] * k[:, :, t, :, None] * v[:, :, t, None, :]
+        n = fg[..., None] * n + ig[..., None] * k[:, :, t]
+        m = mn
+        qs = q[:, :, t] / np.sqrt(dqk)
+        den = np.maximum(np.abs(np.einsum("bhd,bhd->bh", qs, n)), np.exp(-m)) + eps
+        hs.append(np.einsum("bhd,bhdv->bhv", qs, C) / den[..., None])
+    return np.stack(hs, 2), (C, n, m)
+
+
 def test_extreme_gates_stay_finite(ops):
-    """Gates at the soft-cap limits (+-15) over many chunks: no inf/nan, state matches the oracle."""
+    """Gates at the soft-cap limits (+-15) over many chunks: no inf/nan.  Here the fp32 recurrence
+    itself is 1.2e-4 away from exact arithmetic (sums near 1e3 inside exp), so the kernel is held to
+    1e-4 against a float64 evaluation and to 5e-4 against the fp32 oracle."""
     rng = np.random.default_rng(3)
     B, NH, S, dqk, dv = 1, 2, 192, 64, 64
     q, k = (rng.standard_normal((B, NH, S, dqk)).astype(np.float32) for _ in range(2))
@@ -213,9 +233,11 @@ def test_extreme_gates_stay_finite(ops):
     i = rng.choice([-15.0, 0.0, 15.0], size=(B, NH, S)).astype(np.float32)
     f = rng.choice([-15.0, 0.0, 15.0], size=(B, NH, S)).astype(np.float32)
     h_ref, st_ref = xo.mlstm_recurrent(q, k, v, i, f)
+    h64, st64 = recurrent_fp64(q, k, v, i, f)
     h, st = ops.mlstm_chunkwise(*(dev(a) for a in (q, k, v, i, f)))
     assert np.isfinite(host(h)).all()
-    assert relerr(host(h), h_ref) < FP32_TOL and relerr(host(st[0]), st_ref[0]) < FP32_TOL
+    assert relerr(host(h), h64) < FP32_TOL and relerr(host(st[0]), st64[0]) < FP32_TOL
+    assert relerr(host(h), h_ref) < 5e-4 and relerr(host(st[0]), st_ref[0]) < 5e-4
     assert np.abs(host(st[2]) - st_ref[2]).max() < 1e-3
 
 

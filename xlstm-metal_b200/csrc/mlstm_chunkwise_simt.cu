@@ -49,14 +49,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_simt_kernel(Chunkw
     float *sV = sP + LT * LDP;           // [LT][DVT]
     float *sVw = sV + LT * DVT;          // [LT][DVT]  rows scaled by the state-update weights
     float *sFl = sVw + LT * DVT;         // [LT] logsig(f)
-    float *sB = sFl + LT;                // [LT] inclusive cumsum
-    float *sI = sB + LT;                 // [LT] i
+    float *sI = sFl + LT;                // [LT] i
     float *sM = sI + LT;                 // [LT] m_t
     float *sWin = sM + LT;               // [LT] e^{b_t+m-m_t}
     float *sW = sWin + LT;               // [LT] e^{a_t-m'}
     float *sQn = sW + LT;                // [LT] q~ . n
     float *sRow = sQn + LT;              // [LT] row sums of P
     __shared__ float s_m;                // carried stabiliser
+    __shared__ double sBd[LT], sUd[LT], sXd[LT];  // cumsum b, u = i - b, running max x
 
     const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
     const int bh = blockIdx.x, b = bh / p.NH, hd = bh % p.NH;
@@ -89,6 +89,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_simt_kernel(Chunkw
         const float m_old = s_m;
 
         // ---- gates ------------------------------------------------------
+        // With u_s = i_s - b_s and x_t = max(m, max_{s<=t} u_s):  m_t = b_t + x_t, and every
+        // exponent of the chunk is a difference u_s - x_t (or m - x_t).  b can reach
+        // ~1e3 in a chunk of strongly negative forget gates, so u and x are kept
+        // in double: the differences stay exact to fp32 rounding of the result.
         if (tid < LT) {
             const bool valid = tid < Lc;
             sFl[tid] = valid ? logsigmoid(Elem<T>::ld(fb + (int64_t)(t0 + tid) * p.sg[2])) : 0.f;
@@ -96,24 +100,25 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_simt_kernel(Chunkw
         }
         __syncthreads();
         if (tid < LT) {
-            float acc = 0.f;
-            for (int s = 0; s <= tid; ++s) acc += sFl[s];
-            sB[tid] = acc;
+            double acc = 0.0;
+            for (int s = 0; s <= tid; ++s) acc += (double)sFl[s];
+            sBd[tid] = acc;
+            sUd[tid] = (double)sI[tid] - acc;
         }
         __syncthreads();
         if (tid < LT) {
-            float mx = m_old;
-            for (int s = 0; s <= tid; ++s) mx = fmaxf(mx, sI[s] - sB[s]);
-            const float bt = sB[tid];
-            sM[tid] = bt + mx;
-            sWin[tid] = expf(m_old - mx);  // e^{b_t + m - m_t}
+            double mx = (double)m_old;
+            for (int s = 0; s <= tid; ++s) mx = fmax(mx, sUd[s]);
+            sXd[tid] = mx;
+            sM[tid] = (float)(sBd[tid] + mx);
+            sWin[tid] = expf((float)((double)m_old - mx));  // e^{b_t + m - m_t}
             sQn[tid] = 0.f;
         }
         __syncthreads();
-        const float G = sB[LT - 1];
+        const double x_last = sXd[LT - 1];
         const float m_new = sM[LT - 1];
-        const float decay = expf(G + m_old - m_new);
-        if (tid < LT) sW[tid] = expf(G - sB[tid] + sI[tid] - m_new);  // 0 for masked tokens (i = -inf)
+        const float decay = expf((float)((double)m_old - x_last));          // e^{G + m - m'}
+        if (tid < LT) sW[tid] = expf((float)(sUd[tid] - x_last));           // e^{a_t - m'}; 0 for masked tokens
 
         // ---- V tile -----------------------------------------------------
         load_tile<T>(sV, DVT, vb + (int64_t)t0 * p.sv[2], p.sv[2], Lc, col0, dv, DVT);
@@ -218,13 +223,13 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_simt_kernel(Chunkw
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
             const int t = ty + 16 * a;
-            const float bt_mt = sB[t] - sM[t];
+            const double xt = sXd[t];
             float rs = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int s = tx + 16 * c;
                 float pv = 0.f;
-                if (s <= t) pv = sacc[a][c] * p.qscale * expf(bt_mt - sB[s] + sI[s]);
+                if (s <= t) pv = sacc[a][c] * p.qscale * expf((float)(sUd[s] - xt));
                 sP[t * LDP + s] = pv;
                 rs += pv;
             }
@@ -303,7 +308,7 @@ int mlstm_chunkwise_simt(const ChunkwiseParams &p, int dtype, cudaStream_t st) {
          reinterpret_cast<uintptr_t>(p.h)) & mask)
         return XLSTM_ERR_UNSUPPORTED;
     const int dqkp = (p.dqk + KP - 1) / KP * KP;
-    const size_t smem = sizeof(float) * ((size_t)dqkp * DVT + dqkp + 3 * LT * LDP + 2 * LT * DVT + 8 * LT);
+    const size_t smem = sizeof(float) * ((size_t)dqkp * DVT + dqkp + 3 * LT * LDP + 2 * LT * DVT + 7 * LT);
     if (smem > 227 * 1024) return XLSTM_ERR_UNSUPPORTED;
     dim3 grid(p.B * p.NH, (p.dv + DVT - 1) / DVT);
     if (dtype == XLSTM_F32) {

@@ -11,8 +11,22 @@
 
 namespace xl {
 
+// tuning knobs (defaults are the measured best on B200)
+#ifndef XL_STEP_DVT
+#define XL_STEP_DVT 64
+#endif
+#ifndef XL_STEP_THREADS
+#define XL_STEP_THREADS 128
+#endif
+#ifndef XL_STEP_UNROLL
+#define XL_STEP_UNROLL 8
+#endif
+#ifndef XL_STEP_MINB
+#define XL_STEP_MINB 1
+#endif
+
 template <typename T, int DVT, int THREADS, int UNROLL>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, XL_STEP_MINB)
 mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                   const T *__restrict__ ig, const T *__restrict__ fg,
                   const float *C0, const float *__restrict__ n0, const float *__restrict__ m0,
@@ -110,7 +124,7 @@ template <typename T>
 static int mlstm_step_launch(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                              const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
                              float *m1, int BH, int dqk, int dv, float eps, cudaStream_t st) {
-    constexpr int DVT = 64, THREADS = 128, UNROLL = 8;
+    constexpr int DVT = XL_STEP_DVT, THREADS = XL_STEP_THREADS, UNROLL = XL_STEP_UNROLL;
     dim3 grid(BH, (dv + DVT - 1) / DVT);
     size_t smem = sizeof(float) * (2 * (size_t)dqk + (THREADS / (DVT / 4)) * DVT);
     auto kern = mlstm_step_kernel<T, DVT, THREADS, UNROLL>;
@@ -137,7 +151,7 @@ extern "C" int xlstm_mlstm_step(const void *q, const void *k, const void *v, con
     if (C0 && (n1 == n0 || m1 == m0)) return XLSTM_ERR_INVALID;  // other CTAs of the head still read n0/m0
     if (dv % 4 != 0) return XLSTM_ERR_UNSUPPORTED;
     if (dtype != XLSTM_F32 && dtype != XLSTM_BF16) return XLSTM_ERR_UNSUPPORTED;
-    if ((int64_t)B * NH > 2147483647LL || (dv + 63) / 64 > 65535) return XLSTM_ERR_UNSUPPORTED;
+    if ((int64_t)B * NH > 2147483647LL || (dv + XL_STEP_DVT - 1) / XL_STEP_DVT > 65535) return XLSTM_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == XLSTM_F32)
         return xl::mlstm_step_launch<float>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, st);
