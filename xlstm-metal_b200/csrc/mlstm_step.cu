@@ -5,8 +5,9 @@
 // Work split: one CTA owns DVT columns of one head's C for all dqk rows, so
 // the h = q~ . C' reduction never leaves the CTA; the 1 KB normaliser vector is
 // recomputed by every CTA of the head (cheaper than a second pass).  Rows are
-// walked in batches of UNROLL independent 128-bit streaming loads per thread
-// to keep enough bytes in flight for HBM3e.
+// walked in batches of UNROLL independent 128-bit streaming loads per thread,
+// the first batch issued before the gate prologue and each next batch before
+// the current one is consumed, to keep enough bytes in flight for HBM3e.
 #include "common.cuh"
 
 namespace xl {
@@ -16,13 +17,13 @@ namespace xl {
 #define XL_STEP_DVT 64
 #endif
 #ifndef XL_STEP_THREADS
-#define XL_STEP_THREADS 128
+#define XL_STEP_THREADS 256
 #endif
 #ifndef XL_STEP_UNROLL
-#define XL_STEP_UNROLL 8
+#define XL_STEP_UNROLL 4
 #endif
 #ifndef XL_STEP_MINB
-#define XL_STEP_MINB 1
+#define XL_STEP_MINB 4
 #endif
 
 template <typename T, int DVT, int THREADS, int UNROLL>
@@ -45,6 +46,20 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
     const int tile = blockIdx.y;
     const int tid = threadIdx.x;
     const bool has_state = (C0 != nullptr);
+    const int cv = tid % CV, rg = tid / CV;
+    const int col = tile * DVT + cv * 4;
+    const bool active = col < dv;
+    const float *Cin = C0 + (size_t)bh * dqk * dv + col;
+    float *Cout = C1 + (size_t)bh * dqk * dv + col;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    // first batch of state rows: in flight while the prologue below runs
+    float4 c[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int j = rg + u * RG;
+        c[u] = (active && has_state && j < dqk) ? ldg_stream(Cin + (size_t)j * dv) : zero4;
+    }
 
     // stabilised gates (every thread: two exps and a log1p are cheaper than a broadcast)
     const float it = Elem<T>::ld(ig + bh);
@@ -76,20 +91,16 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
         if (tile == 0) m1[bh] = mnew;
     }
 
-    const int cv = tid % CV, rg = tid / CV;
-    const int col = tile * DVT + cv * 4;
-    const bool active = col < dv;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc = zero4;
     if (active) {
         const float4 v4 = ld4(v + (size_t)bh * dv + col);
-        const float *Cin = C0 + (size_t)bh * dqk * dv + col;
-        float *Cout = C1 + (size_t)bh * dqk * dv + col;
         for (int j0 = rg; j0 < dqk; j0 += RG * UNROLL) {
-            float4 c[UNROLL];
+            // next batch goes out before this one is consumed
+            float4 nx[UNROLL];
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const int j = j0 + u * RG;
-                c[u] = (has_state && j < dqk) ? ldg_stream(Cin + (size_t)j * dv) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const int j = j0 + (UNROLL + u) * RG;
+                nx[u] = (has_state && j < dqk) ? ldg_stream(Cin + (size_t)j * dv) : zero4;
             }
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
@@ -108,6 +119,8 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
                     acc.w = fmaf(o.w, qj, acc.w);
                 }
             }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) c[u] = nx[u];
         }
     }
     st4(s_red + rg * DVT + cv * 4, acc);

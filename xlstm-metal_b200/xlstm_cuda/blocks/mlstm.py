@@ -1,0 +1,281 @@
+"""mLSTM cells, neuron and block with the reference's call signatures, backed by the CUDA kernels.
+
+Each class keeps the constructor arguments, attribute names (they are addressed by the
+safetensors key map) and ``forward`` contract of its reference twin:
+
+``mLSTMProjectionCell``      xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/mlstm_projection_cell.py:19-106
+``mLSTMRecurrentKernelCell`` .../mlstm_recurrent_kernel_cell.py:19-161
+``mLSTMParallelKernelCell``  xlstm_metal/mlx_jit/blocks/mlstm/mlstm_chunkwise/mlstm_parallel_kernel_cell.py:110-249
+``mLSTMOutputCell``          .../mlstm_output_cell.py:22-99
+``mLSTMNeuron``              .../mlstm_neuron.py:21-176 (dispatch rule: mlx_jit/.../mlstm_neuron.py:222-264)
+``mLSTMBlock``               xlstm_metal/torch_native/blocks/mlstm/mlstm_block.py:69-283
+
+The projection GEMMs, norms and the SwiGLU FFN are torch (cuBLAS) calls; the recurrence, the
+decode step and the gate soft-cap are the hand-written kernels.  q, k, v travel to the
+chunkwise kernel as strided views of the [B,S,NH,d] projection output: no transposed copy.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..utils import resolve_dtype
+from .rms_norm import MultiHeadRMSNorm, RMSNormCell
+from .soft_cap import SoftCap
+
+State = Tuple[torch.Tensor, torch.Tensor, torch.Tensor]
+
+
+class mLSTMProjectionCell(nn.Module):
+    def __init__(self, input_size: int, num_heads: int, qk_dim_per_head: int, v_dim_per_head: int,
+                 use_bias: bool = False, gate_soft_cap: Optional[float] = None):
+        super().__init__()
+        self.input_size = input_size
+        self.num_heads = num_heads
+        self.qk_dim_per_head = qk_dim_per_head
+        self.v_dim_per_head = v_dim_per_head
+        self.gate_soft_cap = gate_soft_cap
+        self.soft_cap = SoftCap()
+        self.q_proj = nn.Linear(input_size, num_heads * qk_dim_per_head, bias=use_bias)
+        self.k_proj = nn.Linear(input_size, num_heads * qk_dim_per_head, bias=use_bias)
+        self.v_proj = nn.Linear(input_size, num_heads * v_dim_per_head, bias=use_bias)
+        self.igate_proj = nn.Linear(input_size, num_heads)  # gates always carry a bias
+        self.fgate_proj = nn.Linear(input_size, num_heads)
+
+    def forward(self, x: torch.Tensor):
+        B, S, _ = x.shape
+        NH = self.num_heads
+        q = self.q_proj(x).view(B, S, NH, self.qk_dim_per_head).permute(0, 2, 1, 3)
+        k = self.k_proj(x).view(B, S, NH, self.qk_dim_per_head).permute(0, 2, 1, 3)
+        v = self.v_proj(x).view(B, S, NH, self.v_dim_per_head).permute(0, 2, 1, 3)
+        i_preact = self.igate_proj(x)
+        f_preact = self.fgate_proj(x)
+        if self.gate_soft_cap is not None:
+            i_preact = self.soft_cap(i_preact, self.gate_soft_cap)
+            f_preact = self.soft_cap(f_preact, self.gate_soft_cap)
+        return q, k, v, i_preact.permute(0, 2, 1), f_preact.permute(0, 2, 1)
+
+
+class _KernelCellBase(nn.Module):
+    def __init__(self, num_heads, qk_dim_per_head, v_dim_per_head, eps, compute_dtype, state_dtype):
+        super().__init__()
+        self.num_heads = num_heads
+        self.qk_dim_per_head = qk_dim_per_head
+        self.v_dim_per_head = v_dim_per_head
+        self.eps = eps
+        self.compute_dtype = compute_dtype
+        self.state_dtype = state_dtype
+
+    def _cast_in(self, q, k, v, i_preact, f_preact):
+        cd = self.compute_dtype
+        return tuple(t.to(dtype=cd) for t in (q, k, v, i_preact, f_preact))
+
+    def _cast_state(self, st: State) -> State:
+        if self.state_dtype == torch.float32:
+            return st
+        return tuple(s.to(self.state_dtype) for s in st)
+
+
+class mLSTMRecurrentKernelCell(_KernelCellBase):
+    """``cell(q,k,v,i,f,state) -> (h,(C,n,m))``.  One token: the decode-step kernel; several
+    tokens: the chunkwise kernel, which is the same recurrence re-associated."""
+
+    def __init__(self, num_heads: int, qk_dim_per_head: int, v_dim_per_head: int, eps: float = 1e-6,
+                 compute_dtype: torch.dtype = torch.float32, state_dtype: torch.dtype = torch.float32):
+        super().__init__(num_heads, qk_dim_per_head, v_dim_per_head, eps, compute_dtype, state_dtype)
+
+    def forward(self, q, k, v, i_preact, f_preact, state: Optional[State] = None):
+        q, k, v, i_preact, f_preact = self._cast_in(q, k, v, i_preact, f_preact)
+        if q.shape[2] == 1:
+            h, st = ops.mlstm_step(q[:, :, 0], k[:, :, 0], v[:, :, 0], i_preact[:, :, 0], f_preact[:, :, 0],
+                                   state, self.eps)
+            return h.unsqueeze(2), self._cast_state(st)
+        h, st = ops.mlstm_chunkwise(q, k, v, i_preact, f_preact, state, 64, self.eps)
+        return h, self._cast_state(st)
+
+
+class mLSTMParallelKernelCell(_KernelCellBase):
+    """Chunkwise-parallel cell: same contract as the recurrent cell, ``chunk_size`` tokens at a time."""
+
+    def __init__(self, num_heads: int, qk_dim_per_head: int, v_dim_per_head: int, chunk_size: int = 64,
+                 eps: float = 1e-6, compute_dtype: torch.dtype = torch.float32,
+                 state_dtype: torch.dtype = torch.float32):
+        super().__init__(num_heads, qk_dim_per_head, v_dim_per_head, eps, compute_dtype, state_dtype)
+        self.chunk_size = chunk_size
+
+    def forward(self, q, k, v, i_preact, f_preact, state: Optional[State] = None):
+        q, k, v, i_preact, f_preact = self._cast_in(q, k, v, i_preact, f_preact)
+        h, st = ops.mlstm_chunkwise(q, k, v, i_preact, f_preact, state, self.chunk_size, self.eps)
+        return h, self._cast_state(st)
+
+
+class mLSTMOutputCell(nn.Module):
+    def __init__(self, input_size: int, num_heads: int, v_dim_per_head: int, use_bias: bool = False,
+                 eps: float = 1e-6):
+        super().__init__()
+        self.input_size = input_size
+        self.num_heads = num_heads
+        self.v_dim_per_head = v_dim_per_head
+        v_dim = num_heads * v_dim_per_head
+        self.norm = MultiHeadRMSNorm(num_heads=num_heads, head_dim=v_dim_per_head, eps=eps)
+        self.ogate_proj = nn.Linear(input_size, v_dim, bias=use_bias)
+        self.out_proj = nn.Linear(v_dim, input_size, bias=use_bias)
+
+    def forward(self, h: torch.Tensor, x_orig: torch.Tensor) -> torch.Tensor:
+        h_norm = self.norm(h.permute(0, 2, 1, 3))                 # [B,S,NH*DH_v]
+        o_gate = torch.sigmoid(self.ogate_proj(x_orig))           # no soft-cap on the output gate
+        return self.out_proj(h_norm * o_gate)
+
+
+class mLSTMNeuron(nn.Module):
+    def __init__(self, input_size: int, num_heads: int, qk_dim_per_head: int, v_dim_per_head: int,
+                 chunk_size: int = 64, kernel_mode: str = "parallel", use_bias: bool = False, eps: float = 1e-6,
+                 gate_soft_cap: Optional[float] = None, compute_dtype: torch.dtype = torch.float32,
+                 state_dtype: torch.dtype = torch.float32):
+        super().__init__()
+        valid_modes = {"parallel", "recurrent"}
+        if kernel_mode not in valid_modes:
+            raise ValueError(f"Invalid kernel_mode '{kernel_mode}'. Valid options: {sorted(valid_modes)}")
+        self.input_size = input_size
+        self.num_heads = num_heads
+        self.qk_dim_per_head = qk_dim_per_head
+        self.v_dim_per_head = v_dim_per_head
+        self.chunk_size = chunk_size
+        self.kernel_mode = kernel_mode
+        self.eps = eps
+        self.compute_dtype = compute_dtype
+        self.state_dtype = state_dtype
+        self.projection_cell = mLSTMProjectionCell(input_size, num_heads, qk_dim_per_head, v_dim_per_head,
+                                                   use_bias=use_bias, gate_soft_cap=gate_soft_cap)
+        self.parallel_kernel = mLSTMParallelKernelCell(num_heads, qk_dim_per_head, v_dim_per_head, chunk_size, eps,
+                                                       compute_dtype, state_dtype)
+        self.recurrent_kernel = mLSTMRecurrentKernelCell(num_heads, qk_dim_per_head, v_dim_per_head, eps,
+                                                         compute_dtype, state_dtype)
+        self.output_cell = mLSTMOutputCell(input_size, num_heads, v_dim_per_head, use_bias=use_bias, eps=eps)
+
+    @property
+    def state_size(self) -> Tuple[int, int, int]:
+        return (self.num_heads * self.qk_dim_per_head * self.v_dim_per_head,
+                self.num_heads * self.qk_dim_per_head, self.num_heads)
+
+    @property
+    def output_size(self) -> int:
+        return self.input_size
+
+    def forward(self, x: torch.Tensor, state: Optional[State] = None):
+        q, k, v, i_preact, f_preact = self.projection_cell(x)
+        S = q.shape[2]
+        use_parallel = self.kernel_mode == "parallel" and self.chunk_size > 0
+        chunk_tokens = (S // self.chunk_size) * self.chunk_size if use_parallel else 0
+        pieces, cur = [], state
+        if chunk_tokens > 0:
+            sl = slice(0, chunk_tokens)
+            h_par, cur = self.parallel_kernel(q[:, :, sl], k[:, :, sl], v[:, :, sl], i_preact[:, :, sl],
+                                              f_preact[:, :, sl], cur)
+            pieces.append(h_par)
+        if S - chunk_tokens > 0:  # the S mod L tail and every decode token go through the recurrent cell
+            sl = slice(chunk_tokens, S)
+            h_seq, cur = self.recurrent_kernel(q[:, :, sl], k[:, :, sl], v[:, :, sl], i_preact[:, :, sl],
+                                               f_preact[:, :, sl], cur)
+            pieces.append(h_seq)
+        h = pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=2)
+        return self.output_cell(h, x), cur
+
+    def get_config(self) -> dict:
+        return {"input_size": self.input_size, "num_heads": self.num_heads, "qk_dim_per_head": self.qk_dim_per_head,
+                "v_dim_per_head": self.v_dim_per_head, "chunk_size": self.chunk_size, "kernel_mode": self.kernel_mode,
+                "eps": self.eps}
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return ((value + multiple - 1) // multiple) * multiple
+
+
+class mLSTMBlock(nn.Module):
+    """Pre-norm residual mLSTM followed by a pre-norm residual SwiGLU FFN (one xLSTM-7B block)."""
+
+    def __init__(self, block_index: int, embedding_dim: int = 4096, num_heads: int = 8, qk_dim_factor: float = 0.5,
+                 v_dim_factor: float = 1.0, gate_soft_cap: float = 15.0, ffn_proj_factor: float = 2.667,
+                 ffn_round_up_to_multiple_of: int = 64, mlstm_round_up_to_multiple_of: int = 64, chunk_size: int = 64,
+                 kernel_mode: str = "metal_chunkwise", norm_eps: float = 1e-6, use_bias: bool = False, eps: float = 1e-6,
+                 sparsity_mask: Optional[torch.Tensor] = None, compute_dtype: torch.dtype = torch.float32,
+                 state_dtype: torch.dtype = torch.float32, **_ignored) -> None:
+        super().__init__()
+        self.block_index = block_index
+        self.embedding_dim = embedding_dim
+        self.num_heads = num_heads
+        self.eps = eps
+        # per-head dims rounded up to the multiple, as the reference block does
+        self.qk_dim_per_head = _round_up(int(embedding_dim * qk_dim_factor / num_heads), mlstm_round_up_to_multiple_of)
+        self.v_dim_per_head = _round_up(int(embedding_dim * v_dim_factor / num_heads), mlstm_round_up_to_multiple_of)
+        self.hidden_size = num_heads * self.v_dim_per_head
+        self.ffn_hidden_dim = _round_up(int(embedding_dim * ffn_proj_factor), ffn_round_up_to_multiple_of)
+        self.norm_mlstm = RMSNormCell(dims=embedding_dim, eps=norm_eps)
+        # the reference torch block pins "recurrent" because it has no chunkwise kernel; here every
+        # mode other than an explicit "recurrent" selects the chunkwise kernel
+        mode = "recurrent" if kernel_mode == "recurrent" else "parallel"
+        self.mlstm_cell = mLSTMNeuron(input_size=embedding_dim, num_heads=num_heads,
+                                      qk_dim_per_head=self.qk_dim_per_head, v_dim_per_head=self.v_dim_per_head,
+                                      chunk_size=chunk_size, use_bias=use_bias, eps=eps, gate_soft_cap=gate_soft_cap,
+                                      kernel_mode=mode, compute_dtype=compute_dtype, state_dtype=state_dtype)
+        self.norm_ffn = RMSNormCell(dims=embedding_dim, eps=norm_eps)
+        self.ffn_proj_up = nn.Linear(embedding_dim, self.ffn_hidden_dim, bias=use_bias)
+        self.ffn_proj_up_gate = nn.Linear(embedding_dim, self.ffn_hidden_dim, bias=use_bias)
+        self.ffn_proj_down = nn.Linear(self.ffn_hidden_dim, embedding_dim, bias=use_bias)
+        self.gate_soft_cap = gate_soft_cap
+        self.compute_dtype = compute_dtype
+        self.state_dtype = state_dtype
+
+    def forward(self, x: torch.Tensor, state: Optional[State] = None):
+        mlstm_out, new_state = self.mlstm_cell(self.norm_mlstm(x), state)
+        x = x + mlstm_out
+        xn = self.norm_ffn(x)
+        x = x + self.ffn_proj_down(F.silu(self.ffn_proj_up_gate(xn)) * self.ffn_proj_up(xn))
+        return x, new_state
+
+    def get_weight_keys(self) -> Dict[str, str]:
+        p = f"backbone.blocks.{self.block_index}"
+        layer = {"q_proj.weight": "q.weight", "k_proj.weight": "k.weight", "v_proj.weight": "v.weight",
+                 "igate_proj.weight": "igate_preact.weight", "igate_proj.bias": "igate_preact.bias",
+                 "fgate_proj.weight": "fgate_preact.weight", "fgate_proj.bias": "fgate_preact.bias"}
+        keys = {"norm_mlstm.weight": f"{p}.norm_mlstm.weight"}
+        keys.update({f"mlstm_cell.projection_cell.{a}": f"{p}.mlstm_layer.{b}" for a, b in layer.items()})
+        keys.update({
+            "mlstm_cell.output_cell.ogate_proj.weight": f"{p}.mlstm_layer.ogate_preact.weight",
+            "mlstm_cell.output_cell.norm.weight": f"{p}.mlstm_layer.multihead_norm.weight",
+            "mlstm_cell.output_cell.out_proj.weight": f"{p}.mlstm_layer.out_proj.weight",
+            "norm_ffn.weight": f"{p}.norm_ffn.weight",
+            "ffn_proj_up.weight": f"{p}.ffn.proj_up.weight",
+            "ffn_proj_up_gate.weight": f"{p}.ffn.proj_up_gate.weight",
+            "ffn_proj_down.weight": f"{p}.ffn.proj_down.weight",
+        })
+        return keys
+
+    @classmethod
+    def from_config(cls, block_index: int, config: Dict[str, Any], sparsity_mask: Optional[torch.Tensor] = None,
+                    **overrides) -> "mLSTMBlock":
+        compute_dtype = overrides.get("compute_dtype", resolve_dtype(config.get("autocast_kernel_dtype", "float32")))
+        state_dtype = overrides.get("state_dtype", resolve_dtype(config.get("inference_state_dtype", "float32")))
+        return cls(block_index=block_index, embedding_dim=config["embedding_dim"], num_heads=config["num_heads"],
+                   qk_dim_factor=config["qk_dim_factor"], v_dim_factor=config["v_dim_factor"],
+                   gate_soft_cap=config["gate_soft_cap"], ffn_proj_factor=config.get("ffn_proj_factor", 2.667),
+                   ffn_round_up_to_multiple_of=config.get("ffn_round_up_to_multiple_of", 64),
+                   mlstm_round_up_to_multiple_of=config.get("mlstm_round_up_to_multiple_of", 64),
+                   chunk_size=config.get("chunk_size", 64), kernel_mode=config.get("kernel_mode", "metal_chunkwise"),
+                   norm_eps=config.get("norm_eps", 1e-6), use_bias=config.get("use_bias", False),
+                   eps=config.get("eps", 1e-6), sparsity_mask=sparsity_mask, compute_dtype=compute_dtype,
+                   state_dtype=state_dtype)
+
+    def get_config(self) -> Dict[str, Any]:
+        return {"block_index": self.block_index, "embedding_dim": self.embedding_dim, "num_heads": self.num_heads,
+                "qk_dim_per_head": self.qk_dim_per_head, "v_dim_per_head": self.v_dim_per_head,
+                "hidden_size": self.hidden_size, "ffn_hidden_dim": self.ffn_hidden_dim,
+                "gate_soft_cap": self.gate_soft_cap, "eps": self.eps}
+
+
+__all__ = ["mLSTMProjectionCell", "mLSTMRecurrentKernelCell", "mLSTMParallelKernelCell", "mLSTMOutputCell",
+           "mLSTMNeuron", "mLSTMBlock"]
