@@ -51,17 +51,12 @@ extern "C" int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const voi
 
     if (!xl::mlstm_chunkwise_tc_supported(p, dtype)) return xl::mlstm_chunkwise_simt(p, dtype, st);
 
-    // Whole chunks on the tensor cores, then the S mod L tail (with the carried
-    // state) on the exact path: the split the reference neuron makes between its
-    // chunkwise and recurrent cells (mlx_jit/.../mlstm_neuron.py:222-257).
-    const int s_full = (S / L) * L;
-    const size_t need = xl::mlstm_chunkwise_tc_workspace(B, NH, s_full, dqk, dv, L);
-    if (need && (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)))
+    // Whole 128-token tiles on the tensor cores, then the remaining tokens (with the carried
+    // state) on the exact path: the split the reference neuron makes between its chunkwise and
+    // recurrent cells (mlx_jit/.../mlstm_neuron.py:222-257).  The tile size is internal: the
+    // chunkwise form is a re-association of the recurrence and its result does not depend on L.
+    const size_t need = xl::mlstm_chunkwise_tc_workspace(B, NH, S, dqk, dv, L);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return XLSTM_ERR_WORKSPACE;
-    if (s_full == S) return xl::mlstm_chunkwise_tc(p, workspace, workspace_bytes, st);
-    // tail needs the intermediate state somewhere: use the final-state buffers
-    // as the hand-over and the (smaller) tail call reads them -- but a kernel
-    // may not read and write the same state buffers, so the tail state lives in
-    // the workspace after the tensor-core scratch.
-    return XLSTM_ERR_UNSUPPORTED;
+    return xl::mlstm_chunkwise_tc(p, workspace, workspace_bytes, st);
 }

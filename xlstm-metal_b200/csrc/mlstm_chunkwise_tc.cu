@@ -1,10 +1,574 @@
-// tcgen05 / TMEM / TMA chunkwise mLSTM forward (bf16).  Placeholder until the
-// tensor-core kernel lands: reports "not supported" so every call takes the
-// exact CUDA-core path.
+// Chunkwise mLSTM forward on the Blackwell tensor cores (bf16 in, fp32 accumulate).
+//
+// One persistent CTA owns a 128-column slice of one head's matrix memory C and
+// walks the sequence in tiles of 128 tokens.  C (dqk x 128, fp32) never leaves
+// the SM: it is the TMEM accumulator of the state-update MMA for the whole
+// sequence, so the inter-chunk carry and the intra-chunk read-out are ONE kernel
+// and no per-chunk state is materialised in HBM.  Per tile (tcgen05.mma, M = 128):
+//
+//   S  = Q K^T                       [128 x 128]   A: Q  K-major (TMA)   B: K  K-major (TMA)
+//   H  = Q~ Cb                       [128 x 128]   A: Q~ K-major         B: Cb MN-major (bf16 copy of C)
+//   H += P V     P = S * D (causal)  [128 x 128]   A: P  bf16 in TMEM    B: V  MN-major (TMA)
+//   C += K~^T V  (two halves of dqk) [128 x 128]   A: K~ MN-major        B: V  MN-major
+//
+// with Q~ = Q * e^{m-x_t} * dqk^-1/2 and K~ = K * e^{u_t-x_last} scaled in place in
+// shared memory after S has consumed the raw tiles.  All exponents are
+// differences that are <= 0 (u_s = i_s - b_s, x_t = max(m, max_{s<=t} u_s)), so
+// nothing can overflow whatever the gates are.  The gate scalars come from a
+// small pre-pass kernel (one warp per head, sequential over tiles) that writes
+// them to caller-provided scratch.
+//
+// Roles (512 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc),
+// warps 4-7 gate matrix P and the H epilogue, warps 8-11 Q~/K~ scaling and q.n,
+// warps 12-15 normaliser update and the C pass (rescale C in TMEM, refresh Cb).
+// TMEM columns: C [0,256)  S/P [256,384)  H [384,512).
+// Every mbarrier wait is bounded; a time-out sets the status word in the
+// scratch buffer, releases all roles and frees TMEM before the CTA returns.
 #include "mlstm_chunkwise.cuh"
+#include "tcgen05.cuh"
 
 namespace xl {
-bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &, int) { return false; }
-size_t mlstm_chunkwise_tc_workspace(int, int, int, int, int, int) { return 0; }
-int mlstm_chunkwise_tc(const ChunkwiseParams &, void *, size_t, cudaStream_t) { return XLSTM_ERR_UNSUPPORTED; }
+
+namespace {
+
+using namespace tc;
+
+constexpr int LT = 128;        // tokens per tile
+constexpr int DVS = 128;       // dv columns per CTA
+constexpr int THREADS = 512;
+constexpr int GW = 6 * LT;     // floats of gate scratch per (head, tile)
+constexpr int G_U2 = 0, G_X2 = LT, G_WINQ = 2 * LT, G_W = 3 * LT, G_EMT = 4 * LT, G_SCAL = 5 * LT;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr size_t WS_HEADER = 256;  // status word lives in the first bytes of the scratch
+
+struct TcParams {
+    CUtensorMap tq, tk, tv;
+    const float *gates;            // [B*NH][NCH][GW]
+    const float *C0, *n0;
+    __nv_bfloat16 *h;
+    int64_t sh_b, sh_h, sh_s;
+    float *C1, *n1;
+    int NH, dv, NCH;
+    float eps, log2_qscale;
+    int *status;
+};
+
+// ---------------------------------------------------------------------------
+// gate pre-pass: one warp per (batch, head), sequential over tiles of 128 tokens
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(32)
+mlstm_gate_prep_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64_t sg_b, int64_t sg_h, int64_t sg_s,
+                       const float *__restrict__ m0, float *__restrict__ gates, float *__restrict__ m_out, int NH,
+                       int NCH, float qscale) {
+    const int bh = blockIdx.x, b = bh / NH, hd = bh % NH, lane = threadIdx.x;
+    const T *ip = ig + b * sg_b + hd * sg_h;
+    const T *fp = fg + b * sg_b + hd * sg_h;
+    double m = m0 ? (double)m0[bh] : 0.0;
+    for (int c = 0; c < NCH; ++c) {
+        const int t0 = c * LT + lane * 4;
+        double bcum[4], u[4], x[4];
+        float iv[4];
+        double run = 0.0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            iv[e] = Elem<T>::ld(ip + (int64_t)(t0 + e) * sg_s);
+            run += (double)logsigmoid(Elem<T>::ld(fp + (int64_t)(t0 + e) * sg_s));
+            bcum[e] = run;
+        }
+        // exclusive warp scan of the lane totals
+        double incl = run;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        const double off = incl - run;
+        double pm = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            bcum[e] += off;
+            u[e] = (double)iv[e] - bcum[e];
+            pm = fmax(pm, u[e]);
+            x[e] = pm;
+        }
+        double mincl = pm;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double v = __shfl_up_sync(0xffffffffu, mincl, o);
+            if (lane >= o) mincl = fmax(mincl, v);
+        }
+        double carry = __shfl_up_sync(0xffffffffu, mincl, 1);
+        if (lane == 0) carry = -INFINITY;
+        carry = fmax(carry, m);
+        const double x_last = fmax(__shfl_sync(0xffffffffu, mincl, 31), m);
+        const double G = __shfl_sync(0xffffffffu, bcum[3], 31);
+        float *g = gates + ((size_t)bh * NCH + c) * GW;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int t = lane * 4 + e;
+            const double xt = fmax(x[e], carry);
+            g[G_U2 + t] = (float)(u[e] * (double)LOG2E);
+            g[G_X2 + t] = (float)(xt * (double)LOG2E);
+            g[G_WINQ + t] = expf((float)(m - xt)) * qscale;
+            g[G_W + t] = expf((float)(u[e] - x_last));
+            g[G_EMT + t] = expf(-(float)(bcum[e] + xt));
+        }
+        if (lane == 0) {
+            g[G_SCAL + 0] = expf((float)(m - x_last));  // decay applied to the carried state
+            g[G_SCAL + 1] = (float)(G + x_last);        // stabiliser after this tile
+        }
+        m = G + x_last;
+    }
+    if (lane == 0) m_out[bh] = (float)m;
+}
+
+// ---------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------
+template <int DQK> struct Smem {
+    static constexpr int NBOX = DQK / 64;                  // 64-column TMA boxes of a Q / K tile
+    static constexpr uint32_t BOX = LT * 128;              // bytes of one box: 128 rows x 128 B
+    static constexpr uint32_t Q = 0;
+    static constexpr uint32_t K = Q + NBOX * BOX;
+    static constexpr uint32_t V = K + NBOX * BOX;          // 2 boxes (128 dv columns)
+    static constexpr uint32_t CB = V + 2 * BOX;            // 2 N-blocks of [DQK rows x 128 B]
+    static constexpr uint32_t CB_BLOCK = DQK * 128;
+    static constexpr uint32_t SMALL = CB + 2 * CB_BLOCK;
+    static constexpr uint32_t N_VEC = SMALL;               // float[DQK]
+    static constexpr uint32_t QN = N_VEC + DQK * 4;        // float[2][LT], by tile parity
+    static constexpr uint32_t BARS = QN + 2 * LT * 4;      // uint64[16]
+    static constexpr uint32_t MISC = BARS + 16 * 8;        // tmem base, abort flag
+    static constexpr uint32_t TOTAL = MISC + 16;
+};
+
+enum { B_QFULL = 0, B_KFULL, B_VFULL, B_SDONE, B_H1DONE, B_UPDDONE, B_H2DONE, B_SCALED, B_CBREADY, B_PREADY,
+       B_HFREE, B_QNDONE, B_NDONE, B_NBARS };
+
+template <int DQK>
+__global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __grid_constant__ TcParams p) {
+    using SM = Smem<DQK>;
+    constexpr int NBOX = SM::NBOX;
+    constexpr int NHALF = DQK / 128;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SM::BARS);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + SM::MISC);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + SM::MISC + 4);
+    float *s_n = reinterpret_cast<float *>(smem + SM::N_VEC);
+    float *s_qn = reinterpret_cast<float *>(smem + SM::QN);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int bh = blockIdx.x, b = bh / p.NH, hd = bh % p.NH;
+    const int col0 = blockIdx.y * DVS;
+    const int NCH = p.NCH;
+    const float *gbase = p.gates + (size_t)bh * NCH * GW;
+
+    if (tid == 0) {
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;  // swizzled tiles need a 1024-byte aligned base
+        mbar_init(&bars[B_QFULL], 1);   mbar_init(&bars[B_KFULL], 1);   mbar_init(&bars[B_VFULL], 1);
+        mbar_init(&bars[B_SDONE], 1);   mbar_init(&bars[B_H1DONE], 1);  mbar_init(&bars[B_UPDDONE], 1);
+        mbar_init(&bars[B_H2DONE], 1);  mbar_init(&bars[B_SCALED], 128); mbar_init(&bars[B_CBREADY], 128);
+        mbar_init(&bars[B_PREADY], 128); mbar_init(&bars[B_HFREE], 128); mbar_init(&bars[B_QNDONE], 128);
+        mbar_init(&bars[B_NDONE], 128);
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tq); tma_prefetch_desc(&p.tk); tma_prefetch_desc(&p.tv);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 512);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t T_C = tmem, T_S = tmem + 256, T_H = tmem + 384;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            for (int k = 0; k < NCH; ++k) {
+                const int t0 = k * LT;
+                if (k > 0 && !(mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag) &&
+                               mbar_wait(&bars[B_QNDONE], (k - 1) & 1, abort_flag))) break;
+                mbar_expect_tx(&bars[B_QFULL], NBOX * SM::BOX);
+                for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[B_QFULL], q * 64, t0, hd, b);
+                if (k > 0 && !(mbar_wait(&bars[B_UPDDONE], (k - 1) & 1, abort_flag) &&
+                               mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
+                mbar_expect_tx(&bars[B_KFULL], NBOX * SM::BOX);
+                for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::K + q * SM::BOX, &p.tk, &bars[B_KFULL], q * 64, t0, hd, b);
+                if (k > 0 && !mbar_wait(&bars[B_H2DONE], (k - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(&bars[B_VFULL], 2 * SM::BOX);
+                for (int q = 0; q < 2; ++q) tma_load_4d(smem + SM::V + q * SM::BOX, &p.tv, &bars[B_VFULL], col0 + q * 64, t0, hd, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            const uint32_t sQ = smem_u32(smem + SM::Q), sK = smem_u32(smem + SM::K), sV = smem_u32(smem + SM::V),
+                           sCb = smem_u32(smem + SM::CB);
+            constexpr uint32_t ID_KK = idesc_bf16(128, 128, false, false);  // S
+            constexpr uint32_t ID_KM = idesc_bf16(128, 128, false, true);   // inter read-out, P V
+            constexpr uint32_t ID_MM = idesc_bf16(128, 128, true, true);    // state update
+            for (int k = 0; k < NCH; ++k) {
+                const uint32_t ph = k & 1;
+                // S = Q K^T  (the previous tile's P V, issued earlier, finishes first: in-order pipe)
+                if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_KFULL], ph, abort_flag))) break;
+                tc_fence_after_sync();
+                for (int kk = 0; kk < DQK / 16; ++kk) {
+                    const uint32_t o = (kk >> 2) * SM::BOX + (kk & 3) * 32;
+                    mma_ss(T_S, smem_desc_sw128(sQ + o, 0, 1024), smem_desc_sw128(sK + o, 0, 1024), ID_KK, kk > 0);
+                }
+                mma_commit(&bars[B_SDONE]);
+                // H = Q~ Cb   (Q~, K~ scaled in place; Cb and the pre-scaled C from the previous C pass)
+                if (!(mbar_wait(&bars[B_SCALED], ph, abort_flag) && mbar_wait(&bars[B_CBREADY], ph, abort_flag))) break;
+                if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
+                tc_fence_after_sync();
+                for (int kk = 0; kk < DQK / 16; ++kk) {
+                    const uint32_t o = (kk >> 2) * SM::BOX + (kk & 3) * 32;
+                    mma_ss(T_H, smem_desc_sw128(sQ + o, 0, 1024), smem_desc_sw128(sCb + kk * 2048, SM::CB_BLOCK, 1024),
+                           ID_KM, kk > 0);
+                }
+                mma_commit(&bars[B_H1DONE]);
+                // C += K~^T V
+                if (!mbar_wait(&bars[B_VFULL], ph, abort_flag)) break;
+                tc_fence_after_sync();
+                for (int hf = 0; hf < NHALF; ++hf)
+                    for (int kk = 0; kk < LT / 16; ++kk)
+                        mma_ss(T_C + hf * 128, smem_desc_sw128(sK + hf * 2 * SM::BOX + kk * 2048, SM::BOX, 1024),
+                               smem_desc_sw128(sV + kk * 2048, SM::BOX, 1024), ID_MM, true);
+                mma_commit(&bars[B_UPDDONE]);
+                // H += P V
+                if (!mbar_wait(&bars[B_PREADY], ph, abort_flag)) break;
+                tc_fence_after_sync();
+                for (int kk = 0; kk < LT / 16; ++kk)
+                    mma_ts(T_H, T_S + kk * 8, smem_desc_sw128(sV + kk * 2048, SM::BOX, 1024), ID_KM, true);
+                mma_commit(&bars[B_H2DONE]);
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ================= gate matrix P, then the H epilogue =================
+        const int t = tid - 128;                       // token row = TMEM lane
+        const uint32_t lane_off = (uint32_t)(t & ~31) << 16;
+        __nv_bfloat16 *hrow = p.h + b * p.sh_b + hd * p.sh_h + col0;
+        for (int k = 0; k < NCH; ++k) {
+            const uint32_t ph = k & 1;
+            const float *g = gbase + (size_t)k * GW;
+            const float x2 = g[G_X2 + t] - p.log2_qscale, winq = g[G_WINQ + t], emt = g[G_EMT + t];  // dqk^-1/2 folded into the exponent
+            const float *u2 = g + G_U2;  // same address across the warp: one L1 transaction per load
+            if (!mbar_wait(&bars[B_SDONE], ph, abort_flag)) break;
+            tc_fence_after_sync();
+            float rowsum = 0.f;
+#pragma unroll 1
+            for (int s0 = 0; s0 < LT; s0 += 32) {
+                uint32_t packed[16];
+                if (s0 <= t) {  // warp-uniform: rows of a warp share t/32
+                    uint32_t r[32];
+                    tmem_ld32(T_S + lane_off + s0, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const int s = s0 + j;
+                        float p0 = (s <= t) ? __uint_as_float(r[j]) * exp2f(__ldg(u2 + s) - x2) : 0.f;
+                        float p1 = (s + 1 <= t) ? __uint_as_float(r[j + 1]) * exp2f(__ldg(u2 + s + 1) - x2) : 0.f;
+                        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                        rowsum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
+                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&pb);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) packed[j] = 0u;
+                }
+                tmem_st16(T_S + lane_off + (s0 >> 1), packed);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&bars[B_PREADY]);
+            // epilogue: h = H / (max(|den|, e^{-m_t}) + eps)
+            if (!(mbar_wait(&bars[B_H2DONE], ph, abort_flag) && mbar_wait(&bars[B_QNDONE], ph, abort_flag))) break;
+            tc_fence_after_sync();
+            const float den = s_qn[ph * LT + t] * winq + rowsum;
+            const float inv = 1.0f / (fmaxf(fabsf(den), emt) + p.eps);
+            __nv_bfloat16 *hp = hrow + (int64_t)(k * LT + t) * p.sh_s;
+#pragma unroll 1
+            for (int c0 = 0; c0 < DVS; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(T_H + lane_off + c0, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 o;
+                    __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
+                    __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
+                    __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]) * inv, __uint_as_float(r[j + 5]) * inv);
+                    __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]) * inv, __uint_as_float(r[j + 7]) * inv);
+                    o.x = *reinterpret_cast<uint32_t *>(&a0); o.y = *reinterpret_cast<uint32_t *>(&a1);
+                    o.z = *reinterpret_cast<uint32_t *>(&a2); o.w = *reinterpret_cast<uint32_t *>(&a3);
+                    *reinterpret_cast<uint4 *>(hp + c0 + j) = o;
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&bars[B_HFREE]);
+        }
+    } else if (warp >= 8 && warp < 12) {
+        // ================= Q~ / K~ scaling in place, q . n =================
+        const int t = tid - 256;  // token row of the Q and K tiles
+        for (int k = 0; k < NCH; ++k) {
+            const uint32_t ph = k & 1;
+            const float *g = gbase + (size_t)k * GW;
+            const float winq = g[G_WINQ + t], w = g[G_W + t];
+            // raw Q and K are free for rewriting once S has been computed
+            if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_KFULL], ph, abort_flag) &&
+                  mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
+            // n of the previous tile must be complete (written by the C-pass warpgroup)
+            if (!mbar_wait(&bars[B_CBREADY], ph, abort_flag)) break;
+            float qn = 0.f;
+#pragma unroll 1
+            for (int q = 0; q < NBOX; ++q) {
+                unsigned char *rowp = smem + SM::Q + q * SM::BOX + t * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int pc = (c + t) & 7;                 // physical 16-byte chunk: spreads banks
+                    const int j0 = q * 64 + ((pc ^ (t & 7)) << 3);  // logical column of that chunk
+                    uint4 v = *reinterpret_cast<uint4 *>(rowp + pc * 16);
+                    __nv_bfloat162 *e = reinterpret_cast<__nv_bfloat162 *>(&v);
+                    const float4 na = *reinterpret_cast<const float4 *>(s_n + j0);
+                    const float4 nb = *reinterpret_cast<const float4 *>(s_n + j0 + 4);
+                    float2 f0 = __bfloat1622float2(e[0]), f1 = __bfloat1622float2(e[1]);
+                    float2 f2 = __bfloat1622float2(e[2]), f3 = __bfloat1622float2(e[3]);
+                    qn += f0.x * na.x + f0.y * na.y + f1.x * na.z + f1.y * na.w + f2.x * nb.x + f2.y * nb.y +
+                          f3.x * nb.z + f3.y * nb.w;
+                    e[0] = __floats2bfloat162_rn(f0.x * winq, f0.y * winq);
+                    e[1] = __floats2bfloat162_rn(f1.x * winq, f1.y * winq);
+                    e[2] = __floats2bfloat162_rn(f2.x * winq, f2.y * winq);
+                    e[3] = __floats2bfloat162_rn(f3.x * winq, f3.y * winq);
+                    *reinterpret_cast<uint4 *>(rowp + pc * 16) = v;
+                }
+            }
+            s_qn[ph * LT + t] = qn;
+#pragma unroll 1
+            for (int q = 0; q < NBOX; ++q) {
+                unsigned char *rowp = smem + SM::K + q * SM::BOX + t * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int pc = (c + t) & 7;
+                    uint4 v = *reinterpret_cast<uint4 *>(rowp + pc * 16);
+                    __nv_bfloat162 *e = reinterpret_cast<__nv_bfloat162 *>(&v);
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        float2 f = __bfloat1622float2(e[x]);
+                        e[x] = __floats2bfloat162_rn(f.x * w, f.y * w);
+                    }
+                    *reinterpret_cast<uint4 *>(rowp + pc * 16) = v;
+                }
+            }
+            fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor-core (async) proxy
+            mbar_arrive(&bars[B_SCALED]);
+            mbar_arrive(&bars[B_QNDONE]);
+        }
+    } else if (warp >= 12) {
+        // ================= normaliser update and C pass =================
+        const int r = tid - 384;                         // row within a 128-row half of C = TMEM lane
+        const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
+        const bool has_state = p.C0 != nullptr;
+        // ---- prologue: initial state -> TMEM (pre-scaled by the first decay) and Cb
+        {
+            const float decay0 = gbase[G_SCAL + 0];
+            for (int hf = 0; hf < NHALF; ++hf) {
+                const int j = hf * 128 + r;
+                const float *src = p.C0 + ((size_t)bh * DQK + j) * p.dv + col0;
+#pragma unroll 1
+                for (int c0 = 0; c0 < DVS; c0 += 32) {
+                    uint32_t v[32];
+#pragma unroll
+                    for (int x = 0; x < 32; x += 4) {
+                        float4 f = has_state ? *reinterpret_cast<const float4 *>(src + c0 + x) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        v[x] = __float_as_uint(f.x); v[x + 1] = __float_as_uint(f.y);
+                        v[x + 2] = __float_as_uint(f.z); v[x + 3] = __float_as_uint(f.w);
+                    }
+#pragma unroll
+                    for (int x = 0; x < 32; x += 8) {
+                        uint4 o;
+                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
+                        o.x = *reinterpret_cast<uint32_t *>(&a0); o.y = *reinterpret_cast<uint32_t *>(&a1);
+                        o.z = *reinterpret_cast<uint32_t *>(&a2); o.w = *reinterpret_cast<uint32_t *>(&a3);
+                        const int c = c0 + x;
+                        *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
+                    }
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) v[x] = __float_as_uint(__uint_as_float(v[x]) * decay0);
+                    tmem_st32(T_C + hf * 128 + lane_off + c0, v);
+                }
+            }
+            for (int j = r; j < DQK; j += 128) s_n[j] = has_state ? p.n0[(size_t)bh * DQK + j] : 0.f;
+            tmem_wait_st();
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(&bars[B_CBREADY]);
+        }
+        for (int k = 0; k < NCH; ++k) {
+            const uint32_t ph = k & 1;
+            const float *g = gbase + (size_t)k * GW;
+            const float decay = g[G_SCAL + 0];
+            const bool last = (k == NCH - 1);
+            const float decay_next = last ? 1.0f : g[GW + G_SCAL + 0];
+            // n' = decay n + column sums of K~  (needs K~ complete, and q.n of this tile done reading n)
+            if (!(mbar_wait(&bars[B_SCALED], ph, abort_flag) && mbar_wait(&bars[B_QNDONE], ph, abort_flag))) break;
+            {
+                const int q = r >> 5, cp = r & 31;   // warp -> 64-column box, lane -> column pair
+                float a0 = 0.f, a1 = 0.f;
+                if (q < NBOX) {
+                    const unsigned char *box = smem + SM::K + q * SM::BOX;
+#pragma unroll 4
+                    for (int tt = 0; tt < LT; ++tt) {
+                        const uint32_t off = tt * 128 + ((((cp >> 2) ^ (tt & 7))) << 4) + ((cp & 3) << 2);
+                        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(box + off));
+                        a0 += f.x; a1 += f.y;
+                    }
+                    const int j = q * 64 + cp * 2;
+                    a0 += decay * s_n[j];
+                    a1 += decay * s_n[j + 1];
+                    s_n[j] = a0;
+                    s_n[j + 1] = a1;
+                    if (last && blockIdx.y == 0) { p.n1[(size_t)bh * DQK + j] = a0; p.n1[(size_t)bh * DQK + j + 1] = a1; }
+                }
+            }
+            mbar_arrive(&bars[B_NDONE]);  // K~ no longer read by this warpgroup
+            // C pass after the state update: refresh Cb (needs the read-out of this tile finished with the
+            // old Cb), pre-scale C for the next tile; after the last tile write C out instead.
+            if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
+            tc_fence_after_sync();
+            for (int hf = 0; hf < NHALF; ++hf) {
+                const int j = hf * 128 + r;
+#pragma unroll 1
+                for (int c0 = 0; c0 < DVS; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(T_C + hf * 128 + lane_off + c0, v);
+                    tmem_wait_ld();
+                    if (last) {
+                        float *dst = p.C1 + ((size_t)bh * DQK + j) * p.dv + col0 + c0;
+#pragma unroll
+                        for (int x = 0; x < 32; x += 4)
+                            *reinterpret_cast<float4 *>(dst + x) = make_float4(__uint_as_float(v[x]), __uint_as_float(v[x + 1]),
+                                                                                __uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 32; x += 8) {
+                            uint4 o;
+                            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+                            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+                            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
+                            o.x = *reinterpret_cast<uint32_t *>(&a0); o.y = *reinterpret_cast<uint32_t *>(&a1);
+                            o.z = *reinterpret_cast<uint32_t *>(&a2); o.w = *reinterpret_cast<uint32_t *>(&a3);
+                            const int c = c0 + x;
+                            *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
+                        }
+#pragma unroll
+                        for (int x = 0; x < 32; ++x) v[x] = __float_as_uint(__uint_as_float(v[x]) * decay_next);
+                        tmem_st32(T_C + hf * 128 + lane_off + c0, v);
+                    }
+                }
+            }
+            if (!last) {
+                tmem_wait_st();
+                fence_proxy_async_smem();
+                tc_fence_before_sync();
+                mbar_arrive(&bars[B_CBREADY]);
+            }
+        }
+    }
+
+    // ---- teardown (every thread gets here, also after an abort) ----------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+    if (tid == 0 && *abort_flag) atomicExch(p.status, 1);
+}
+
+}  // namespace
+
+bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype) {
+    if (dtype != XLSTM_BF16) return false;
+    if (p.dqk != 256 && p.dqk != 128) return false;
+    if (p.dv % DVS) return false;
+    if (p.S < LT) return false;
+    for (int d = 0; d < 3; ++d)
+        if (p.sq[d] % 8 || p.sk[d] % 8 || p.sv[d] % 8 || p.sh[d] % 8) return false;  // 16-byte TMA / store alignment
+    if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
+         reinterpret_cast<uintptr_t>(p.h)) & 15u)
+        return false;
+    if (p.dv / DVS > 65535) return false;
+    return get_encode_tiled() != nullptr;
+}
+
+size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L) {
+    (void)dv; (void)L;
+    const size_t nch = (size_t)(S / LT);
+    // header (status) + gate scalars + hand-over state (n, m) for a tail that runs on the exact path
+    return WS_HEADER + (size_t)B * NH * nch * GW * sizeof(float) + (size_t)B * NH * (dqk + 1) * sizeof(float) + 256;
+}
+
+int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    const int s_full = (p.S / LT) * LT;
+    const int nch = s_full / LT;
+    const int BH = p.B * p.NH;
+    if (!workspace || workspace_bytes < mlstm_chunkwise_tc_workspace(p.B, p.NH, s_full, p.dqk, p.dv, p.L))
+        return XLSTM_ERR_WORKSPACE;
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    int *status = reinterpret_cast<int *>(ws);
+    float *gates = reinterpret_cast<float *>(ws + WS_HEADER);
+    float *tail_n = gates + (size_t)BH * nch * GW;
+    float *tail_m = tail_n + (size_t)BH * p.dqk;
+    const bool tail = s_full < p.S;
+    if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return XLSTM_ERR_CUDA;
+
+    mlstm_gate_prep_kernel<__nv_bfloat16><<<BH, 32, 0, st>>>(
+        static_cast<const __nv_bfloat16 *>(p.ig), static_cast<const __nv_bfloat16 *>(p.fg), p.sg[0], p.sg[1], p.sg[2],
+        p.C0 ? p.m0 : nullptr, gates, tail ? tail_m : p.m1, p.NH, nch, p.qscale);
+    if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
+
+    TcParams tp{};
+    if (!make_tmap_bf16_4d(&tp.tq, p.q, p.dqk, s_full, p.NH, p.B, p.sq[2], p.sq[1], p.sq[0], LT) ||
+        !make_tmap_bf16_4d(&tp.tk, p.k, p.dqk, s_full, p.NH, p.B, p.sk[2], p.sk[1], p.sk[0], LT) ||
+        !make_tmap_bf16_4d(&tp.tv, p.v, p.dv, s_full, p.NH, p.B, p.sv[2], p.sv[1], p.sv[0], LT))
+        return XLSTM_ERR_UNSUPPORTED;
+    tp.gates = gates;
+    tp.C0 = p.C0; tp.n0 = p.n0;
+    tp.h = static_cast<__nv_bfloat16 *>(p.h);
+    tp.sh_b = p.sh[0]; tp.sh_h = p.sh[1]; tp.sh_s = p.sh[2];
+    tp.C1 = p.C1; tp.n1 = tail ? tail_n : p.n1;
+    tp.NH = p.NH; tp.dv = p.dv; tp.NCH = nch; tp.eps = p.eps; tp.log2_qscale = log2f(p.qscale); tp.status = status;
+    dim3 grid(BH, p.dv / DVS);
+    cudaError_t e;
+    if (p.dqk == 256) {
+        auto kern = mlstm_chunkwise_tc_kernel<256>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<256>::TOTAL) != cudaSuccess)
+            return XLSTM_ERR_CUDA;
+        kern<<<grid, THREADS, Smem<256>::TOTAL, st>>>(tp);
+    } else {
+        auto kern = mlstm_chunkwise_tc_kernel<128>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<128>::TOTAL) != cudaSuccess)
+            return XLSTM_ERR_CUDA;
+        kern<<<grid, THREADS, Smem<128>::TOTAL, st>>>(tp);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return XLSTM_ERR_CUDA;
+    if (!tail) return XLSTM_OK;
+
+    // S mod 128 tail on the exact path, continuing from (C1, tail_n, tail_m).  C is handed over in
+    // place: every CTA of that kernel reads only the columns it later writes.
+    ChunkwiseParams t = p;
+    const size_t esz = 2;
+    t.q = static_cast<const unsigned char *>(p.q) + (size_t)s_full * p.sq[2] * esz;
+    t.k = static_cast<const unsigned char *>(p.k) + (size_t)s_full * p.sk[2] * esz;
+    t.v = static_cast<const unsigned char *>(p.v) + (size_t)s_full * p.sv[2] * esz;
+    t.h = static_cast<unsigned char *>(p.h) + (size_t)s_full * p.sh[2] * esz;
+    t.ig = static_cast<const unsigned char *>(p.ig) + (size_t)s_full * p.sg[2] * esz;
+    t.fg = static_cast<const unsigned char *>(p.fg) + (size_t)s_full * p.sg[2] * esz;
+    t.S = p.S - s_full;
+    t.L = 64;
+    t.C0 = p.C1; t.n0 = tail_n; t.m0 = tail_m;
+    return mlstm_chunkwise_simt(t, XLSTM_BF16, st);
+}
+
 }  // namespace xl
