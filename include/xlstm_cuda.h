@@ -36,7 +36,8 @@ typedef enum {
     XLSTM_ERR_UNSUPPORTED = -2,  /* shape or dtype outside what the kernels cover */
     XLSTM_ERR_CUDA = -3,         /* a CUDA runtime call or launch failed */
     XLSTM_ERR_WORKSPACE = -4,    /* caller-provided scratch is too small or misaligned */
-    XLSTM_ERR_TIMEOUT = -5       /* a bounded device-side wait gave up (status word set) */
+    XLSTM_ERR_TIMEOUT = -5,      /* a bounded device-side wait gave up (status word set) */
+    XLSTM_ERR_STATIC_SCRATCH = -6 /* problem needs more scratch than the library's built-in block holds */
 } xlstm_status;
 
 int xlstm_version(void);
@@ -95,6 +96,22 @@ int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const void *v, const
                               const int64_t *strides, void *workspace, size_t workspace_bytes, void *stream);
 
 size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int dv, int L, int dtype);
+
+/*
+ * xlstm_mlstm_chunkwise_fwd for callers that cannot supply scratch memory (no counterpart in
+ * the reference: its launchers allocate their outputs through the framework).  Same arguments
+ * and results as xlstm_mlstm_chunkwise_fwd without `workspace`; the scratch is an 8 MiB block
+ * built into the library image (present on every GPU that loads the library, until exit).
+ * It covers B*NH*(S/128) <= ~2700 tiles, e.g. one 32k-token prompt at NH = 8; larger problems
+ * return XLSTM_ERR_STATIC_SCRATCH.  Calls cudaMalloc / cudaFree never.  The first call on a
+ * device resolves the block's address and should precede any stream capture.  All calls on a
+ * device share the block: do not let two of them overlap on the GPU.
+ */
+int xlstm_mlstm_chunkwise_fwd_static(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                     const float *C0, const float *n0, const float *m0,
+                                     void *h, float *C1, float *n1, float *m1,
+                                     int B, int NH, int S, int dqk, int dv, int L, float eps, int dtype,
+                                     const int64_t *strides, void *stream);
 
 /*
  * Packaged sLSTM cell (scalar gates per head, state c,n,m) applied to S

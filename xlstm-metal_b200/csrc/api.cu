@@ -11,6 +11,7 @@ extern "C" const char *xlstm_strerror(int status) {
         case XLSTM_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
         case XLSTM_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
         case XLSTM_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case XLSTM_ERR_STATIC_SCRATCH: return "problem needs more scratch than the built-in static block holds; use the workspace entry point";
         default: return "unknown status";
     }
 }
