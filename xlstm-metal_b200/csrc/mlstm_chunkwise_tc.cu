@@ -18,9 +18,10 @@
 // small pre-pass kernel (one warp per head, sequential over tiles) that writes
 // them to caller-provided scratch.
 //
-// Roles (512 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc),
-// warps 4-7 gate matrix P and the H epilogue, warps 8-11 Q~/K~ scaling and q.n,
-// warps 12-15 normaliser update and the C pass (rescale C in TMEM, refresh Cb).
+// Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc),
+// warps 4-7 gate matrix P and the denominators, warps 8-11 Q~ scaling and q.n,
+// warps 12-15 K~ scaling and the C pass (rescale C in TMEM, refresh Cb),
+// warps 16-19 normaliser update and the H epilogue.
 // TMEM columns: C [0,256)  S/P [256,384)  H [384,512).
 // Every mbarrier wait is bounded; a time-out sets the status word in the
 // scratch buffer, releases all roles and frees TMEM before the CTA returns.
@@ -35,11 +36,18 @@ using namespace tc;
 
 constexpr int LT = 128;        // tokens per tile
 constexpr int DVS = 128;       // dv columns per CTA
-constexpr int THREADS = 512;
+constexpr int THREADS = 640;
 constexpr int GW = 6 * LT;     // floats of gate scratch per (head, tile)
 constexpr int G_U2 = 0, G_X2 = LT, G_WINQ = 2 * LT, G_W = 3 * LT, G_EMT = 4 * LT, G_SCAL = 5 * LT;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr size_t WS_HEADER = 256;  // status word lives in the first bytes of the scratch
+
+#ifdef XL_TC_TRACE
+__device__ long long g_trace[64 * 32];
+#define TRACE(id) do { if (blockIdx.x == 0 && blockIdx.y == 0 && k < 64) g_trace[k * 32 + (id)] = clock64(); } while (0)
+#else
+#define TRACE(id) do { } while (0)
+#endif
 
 struct TcParams {
     CUtensorMap tq, tk, tv;
@@ -135,15 +143,34 @@ template <int DQK> struct Smem {
     static constexpr uint32_t CB = V + 2 * BOX;            // 2 N-blocks of [DQK rows x 128 B]
     static constexpr uint32_t CB_BLOCK = DQK * 128;
     static constexpr uint32_t SMALL = CB + 2 * CB_BLOCK;
-    static constexpr uint32_t N_VEC = SMALL;               // float[DQK]
-    static constexpr uint32_t QN = N_VEC + DQK * 4;        // float[2][LT], by tile parity
-    static constexpr uint32_t BARS = QN + 2 * LT * 4;      // uint64[16]
+    static constexpr uint32_t N_VEC = SMALL;               // float[DQK]   normaliser n
+    static constexpr uint32_t QN = N_VEC + DQK * 4;        // float[LT]    q . n of the current tile
+    static constexpr uint32_t INV = QN + LT * 4;           // float[2][LT] row sums of P, by tile parity
+    static constexpr uint32_t BARS = INV + 2 * LT * 4;     // uint64[16]
     static constexpr uint32_t MISC = BARS + 16 * 8;        // tmem base, abort flag
     static constexpr uint32_t TOTAL = MISC + 16;
 };
 
-enum { B_QFULL = 0, B_KFULL, B_VFULL, B_SDONE, B_H1DONE, B_UPDDONE, B_H2DONE, B_SCALED, B_CBREADY, B_PREADY,
-       B_HFREE, B_QNDONE, B_NDONE, B_NBARS };
+enum { B_QFULL = 0, B_KFULL, B_VFULL, B_SDONE, B_H1DONE, B_UPDDONE, B_H2DONE, B_QSCALED, B_KSCALED, B_CBREADY,
+       B_PREADY, B_HFREE, B_NDONE, B_NBARS };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+// packed bf16 x bf16 -> bf16 (one rounding); `w2` holds the same bf16 scale in both halves
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t w2) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&w2));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
 
 template <int DQK>
 __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __grid_constant__ TcParams p) {
@@ -156,6 +183,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + SM::MISC + 4);
     float *s_n = reinterpret_cast<float *>(smem + SM::N_VEC);
     float *s_qn = reinterpret_cast<float *>(smem + SM::QN);
+    float *s_rs = reinterpret_cast<float *>(smem + SM::INV);   // row sums of P, by tile parity
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x, b = bh / p.NH, hd = bh % p.NH;
@@ -167,9 +195,9 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;  // swizzled tiles need a 1024-byte aligned base
         mbar_init(&bars[B_QFULL], 1);   mbar_init(&bars[B_KFULL], 1);   mbar_init(&bars[B_VFULL], 1);
         mbar_init(&bars[B_SDONE], 1);   mbar_init(&bars[B_H1DONE], 1);  mbar_init(&bars[B_UPDDONE], 1);
-        mbar_init(&bars[B_H2DONE], 1);  mbar_init(&bars[B_SCALED], 128); mbar_init(&bars[B_CBREADY], 128);
-        mbar_init(&bars[B_PREADY], 128); mbar_init(&bars[B_HFREE], 128); mbar_init(&bars[B_QNDONE], 128);
-        mbar_init(&bars[B_NDONE], 128);
+        mbar_init(&bars[B_H2DONE], 1);
+        mbar_init(&bars[B_QSCALED], 128); mbar_init(&bars[B_KSCALED], 128); mbar_init(&bars[B_CBREADY], 128);
+        mbar_init(&bars[B_PREADY], 128);  mbar_init(&bars[B_HFREE], 128);   mbar_init(&bars[B_NDONE], 128);
         mbar_fence_init();
         tma_prefetch_desc(&p.tq); tma_prefetch_desc(&p.tk); tma_prefetch_desc(&p.tv);
     }
@@ -182,18 +210,23 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
 
     if (warp == 0) {
         // ================= TMA producer =================
+        // Q is free once the read-out MMA of the previous tile has run (and the scaling warps are
+        // done with it: they finish before that MMA is issued); K once the state update has run
+        // and the normaliser sums are taken; V once both its consumers (update, P V) have run.
         if (lane == 0) {
             for (int k = 0; k < NCH; ++k) {
                 const int t0 = k * LT;
-                if (k > 0 && !(mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag) &&
-                               mbar_wait(&bars[B_QNDONE], (k - 1) & 1, abort_flag))) break;
+                if (k > 0 && !mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag)) break;
+                TRACE(16);
                 mbar_expect_tx(&bars[B_QFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[B_QFULL], q * 64, t0, hd, b);
                 if (k > 0 && !(mbar_wait(&bars[B_UPDDONE], (k - 1) & 1, abort_flag) &&
                                mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
+                TRACE(17);
                 mbar_expect_tx(&bars[B_KFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::K + q * SM::BOX, &p.tk, &bars[B_KFULL], q * 64, t0, hd, b);
                 if (k > 0 && !mbar_wait(&bars[B_H2DONE], (k - 1) & 1, abort_flag)) break;
+                TRACE(18);
                 mbar_expect_tx(&bars[B_VFULL], 2 * SM::BOX);
                 for (int q = 0; q < 2; ++q) tma_load_4d(smem + SM::V + q * SM::BOX, &p.tv, &bars[B_VFULL], col0 + q * 64, t0, hd, b);
             }
@@ -201,75 +234,98 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            const uint32_t sQ = smem_u32(smem + SM::Q), sK = smem_u32(smem + SM::K), sV = smem_u32(smem + SM::V),
-                           sCb = smem_u32(smem + SM::CB);
             constexpr uint32_t ID_KK = idesc_bf16(128, 128, false, false);  // S
             constexpr uint32_t ID_KM = idesc_bf16(128, 128, false, true);   // inter read-out, P V
             constexpr uint32_t ID_MM = idesc_bf16(128, 128, true, true);    // state update
+            // descriptors differ only in the start address (low word, units of 16 bytes)
+            const uint64_t dQ = smem_desc_sw128(smem_u32(smem + SM::Q), 0, 1024);
+            const uint64_t dK = smem_desc_sw128(smem_u32(smem + SM::K), 0, 1024);
+            const uint64_t dCb = smem_desc_sw128(smem_u32(smem + SM::CB), SM::CB_BLOCK, 1024);
+            const uint64_t dKm = smem_desc_sw128(smem_u32(smem + SM::K), SM::BOX, 1024);
+            const uint64_t dV = smem_desc_sw128(smem_u32(smem + SM::V), SM::BOX, 1024);
             for (int k = 0; k < NCH; ++k) {
                 const uint32_t ph = k & 1;
+                TRACE(0);
                 // S = Q K^T  (the previous tile's P V, issued earlier, finishes first: in-order pipe)
                 if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_KFULL], ph, abort_flag))) break;
                 tc_fence_after_sync();
+                TRACE(1);
+#pragma unroll
                 for (int kk = 0; kk < DQK / 16; ++kk) {
-                    const uint32_t o = (kk >> 2) * SM::BOX + (kk & 3) * 32;
-                    mma_ss(T_S, smem_desc_sw128(sQ + o, 0, 1024), smem_desc_sw128(sK + o, 0, 1024), ID_KK, kk > 0);
+                    const uint32_t o = ((kk >> 2) * SM::BOX + (kk & 3) * 32) >> 4;
+                    mma_ss(T_S, dQ + o, dK + o, ID_KK, kk > 0);
                 }
                 mma_commit(&bars[B_SDONE]);
-                // H = Q~ Cb   (Q~, K~ scaled in place; Cb and the pre-scaled C from the previous C pass)
-                if (!(mbar_wait(&bars[B_SCALED], ph, abort_flag) && mbar_wait(&bars[B_CBREADY], ph, abort_flag))) break;
+                // H = Q~ Cb   (Q~ scaled in place; Cb and the pre-scaled C from the previous C pass)
+                if (!(mbar_wait(&bars[B_QSCALED], ph, abort_flag) && mbar_wait(&bars[B_CBREADY], ph, abort_flag))) break;
                 if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
                 tc_fence_after_sync();
+                TRACE(2);
+#pragma unroll
                 for (int kk = 0; kk < DQK / 16; ++kk) {
-                    const uint32_t o = (kk >> 2) * SM::BOX + (kk & 3) * 32;
-                    mma_ss(T_H, smem_desc_sw128(sQ + o, 0, 1024), smem_desc_sw128(sCb + kk * 2048, SM::CB_BLOCK, 1024),
-                           ID_KM, kk > 0);
+                    const uint32_t o = ((kk >> 2) * SM::BOX + (kk & 3) * 32) >> 4;
+                    mma_ss(T_H, dQ + o, dCb + kk * (2048 >> 4), ID_KM, kk > 0);
                 }
                 mma_commit(&bars[B_H1DONE]);
                 // C += K~^T V
-                if (!mbar_wait(&bars[B_VFULL], ph, abort_flag)) break;
+                if (!(mbar_wait(&bars[B_KSCALED], ph, abort_flag) && mbar_wait(&bars[B_VFULL], ph, abort_flag))) break;
                 tc_fence_after_sync();
+                TRACE(3);
+#pragma unroll
                 for (int hf = 0; hf < NHALF; ++hf)
+#pragma unroll
                     for (int kk = 0; kk < LT / 16; ++kk)
-                        mma_ss(T_C + hf * 128, smem_desc_sw128(sK + hf * 2 * SM::BOX + kk * 2048, SM::BOX, 1024),
-                               smem_desc_sw128(sV + kk * 2048, SM::BOX, 1024), ID_MM, true);
+                        mma_ss(T_C + hf * 128, dKm + ((hf * 2 * SM::BOX + kk * 2048) >> 4), dV + kk * (2048 >> 4), ID_MM, true);
                 mma_commit(&bars[B_UPDDONE]);
                 // H += P V
                 if (!mbar_wait(&bars[B_PREADY], ph, abort_flag)) break;
                 tc_fence_after_sync();
-                for (int kk = 0; kk < LT / 16; ++kk)
-                    mma_ts(T_H, T_S + kk * 8, smem_desc_sw128(sV + kk * 2048, SM::BOX, 1024), ID_KM, true);
+                TRACE(4);
+#pragma unroll
+                for (int kk = 0; kk < LT / 16; ++kk) mma_ts(T_H, T_S + kk * 8, dV + kk * (2048 >> 4), ID_KM, true);
                 mma_commit(&bars[B_H2DONE]);
             }
         }
-    } else if (warp >= 4 && warp < 8) {
-        // ================= gate matrix P, then the H epilogue =================
+    }
+    else if (warp >= 4 && warp < 8) {
+        // ================= gate matrix P = S * D and the denominators =================
         const int t = tid - 128;                       // token row = TMEM lane
-        const uint32_t lane_off = (uint32_t)(t & ~31) << 16;
-        __nv_bfloat16 *hrow = p.h + b * p.sh_b + hd * p.sh_h + col0;
+        const int t0w = t & ~31;                       // first row of this warp
+        const uint32_t lane_off = (uint32_t)t0w << 16;
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
             const float *g = gbase + (size_t)k * GW;
-            const float x2 = g[G_X2 + t] - p.log2_qscale, winq = g[G_WINQ + t], emt = g[G_EMT + t];  // dqk^-1/2 folded into the exponent
-            const float *u2 = g + G_U2;  // same address across the warp: one L1 transaction per load
+            const float x2 = g[G_X2 + t] - p.log2_qscale;  // dqk^-1/2 folded into the exponent
+            float u2v[4];                                  // lane holds u2 of column s0 + lane
+#pragma unroll
+            for (int pc = 0; pc < 4; ++pc) u2v[pc] = g[G_U2 + pc * 32 + lane];
             if (!mbar_wait(&bars[B_SDONE], ph, abort_flag)) break;
             tc_fence_after_sync();
+            if (t == 0) TRACE(5);
             float rowsum = 0.f;
-#pragma unroll 1
-            for (int s0 = 0; s0 < LT; s0 += 32) {
+#pragma unroll
+            for (int pc = 0; pc < 4; ++pc) {
+                const int s0 = pc * 32;
                 uint32_t packed[16];
-                if (s0 <= t) {  // warp-uniform: rows of a warp share t/32
+                if (s0 <= t0w) {  // warp-uniform; columns beyond the warp's rows are all masked
                     uint32_t r[32];
                     tmem_ld32(T_S + lane_off + s0, r);
                     tmem_wait_ld();
+                    const bool diag = (s0 == t0w);
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        const int s = s0 + j;
-                        float p0 = (s <= t) ? __uint_as_float(r[j]) * exp2f(__ldg(u2 + s) - x2) : 0.f;
-                        float p1 = (s + 1 <= t) ? __uint_as_float(r[j + 1]) * exp2f(__ldg(u2 + s + 1) - x2) : 0.f;
-                        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-                        rowsum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
-                        packed[j >> 1] = *reinterpret_cast<uint32_t *>(&pb);
+                        const float ua = __shfl_sync(0xffffffffu, u2v[pc], j);
+                        const float ub = __shfl_sync(0xffffffffu, u2v[pc], j + 1);
+                        float p0 = __uint_as_float(r[j]) * ex2_approx(ua - x2);
+                        float p1 = __uint_as_float(r[j + 1]) * ex2_approx(ub - x2);
+                        if (diag) {
+                            if (j > lane) p0 = 0.f;
+                            if (j + 1 > lane) p1 = 0.f;
+                        }
+                        const uint32_t pk = pack_bf16(p0, p1);
+                        const float2 pr = unpack_bf16(pk);
+                        rowsum += pr.x + pr.y;
+                        packed[j >> 1] = pk;
                     }
                 } else {
 #pragma unroll
@@ -278,96 +334,57 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 tmem_st16(T_S + lane_off + (s0 >> 1), packed);
             }
             tmem_wait_st();
+            s_rs[ph * LT + t] = rowsum;   // read by the epilogue warps after PREADY
             tc_fence_before_sync();
             mbar_arrive(&bars[B_PREADY]);
-            // epilogue: h = H / (max(|den|, e^{-m_t}) + eps)
-            if (!(mbar_wait(&bars[B_H2DONE], ph, abort_flag) && mbar_wait(&bars[B_QNDONE], ph, abort_flag))) break;
-            tc_fence_after_sync();
-            const float den = s_qn[ph * LT + t] * winq + rowsum;
-            const float inv = 1.0f / (fmaxf(fabsf(den), emt) + p.eps);
-            __nv_bfloat16 *hp = hrow + (int64_t)(k * LT + t) * p.sh_s;
-#pragma unroll 1
-            for (int c0 = 0; c0 < DVS; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(T_H + lane_off + c0, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    uint4 o;
-                    __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(r[j]) * inv, __uint_as_float(r[j + 1]) * inv);
-                    __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]) * inv, __uint_as_float(r[j + 3]) * inv);
-                    __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]) * inv, __uint_as_float(r[j + 5]) * inv);
-                    __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]) * inv, __uint_as_float(r[j + 7]) * inv);
-                    o.x = *reinterpret_cast<uint32_t *>(&a0); o.y = *reinterpret_cast<uint32_t *>(&a1);
-                    o.z = *reinterpret_cast<uint32_t *>(&a2); o.w = *reinterpret_cast<uint32_t *>(&a3);
-                    *reinterpret_cast<uint4 *>(hp + c0 + j) = o;
-                }
-            }
-            tc_fence_before_sync();
-            mbar_arrive(&bars[B_HFREE]);
+            if (t == 0) TRACE(6);
         }
     } else if (warp >= 8 && warp < 12) {
-        // ================= Q~ / K~ scaling in place, q . n =================
-        const int t = tid - 256;  // token row of the Q and K tiles
+        // ================= Q~ = Q * e^{m-x_t} dqk^-1/2 in place, q . n =================
+        const int t = tid - 256;
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
-            const float *g = gbase + (size_t)k * GW;
-            const float winq = g[G_WINQ + t], w = g[G_W + t];
-            // raw Q and K are free for rewriting once S has been computed
-            if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_KFULL], ph, abort_flag) &&
-                  mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
-            // n of the previous tile must be complete (written by the C-pass warpgroup)
-            if (!mbar_wait(&bars[B_CBREADY], ph, abort_flag)) break;
-            float qn = 0.f;
+            const uint32_t w2 = pack_bf16(gbase[(size_t)k * GW + G_WINQ + t], gbase[(size_t)k * GW + G_WINQ + t]);
+            if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
+            // n of the previous tile complete (tile 0: written by the prologue)
+            if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
+            if (t == 0) TRACE(9);
+            float qn0 = 0.f, qn1 = 0.f;
 #pragma unroll 1
             for (int q = 0; q < NBOX; ++q) {
                 unsigned char *rowp = smem + SM::Q + q * SM::BOX + t * 128;
+                uint4 v[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(rowp + (((c + t) & 7) << 4));
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const int pc = (c + t) & 7;                 // physical 16-byte chunk: spreads banks
+                    const int pc = (c + t) & 7;                    // physical 16-byte chunk (rotation spreads banks)
                     const int j0 = q * 64 + ((pc ^ (t & 7)) << 3);  // logical column of that chunk
-                    uint4 v = *reinterpret_cast<uint4 *>(rowp + pc * 16);
-                    __nv_bfloat162 *e = reinterpret_cast<__nv_bfloat162 *>(&v);
                     const float4 na = *reinterpret_cast<const float4 *>(s_n + j0);
                     const float4 nb = *reinterpret_cast<const float4 *>(s_n + j0 + 4);
-                    float2 f0 = __bfloat1622float2(e[0]), f1 = __bfloat1622float2(e[1]);
-                    float2 f2 = __bfloat1622float2(e[2]), f3 = __bfloat1622float2(e[3]);
-                    qn += f0.x * na.x + f0.y * na.y + f1.x * na.z + f1.y * na.w + f2.x * nb.x + f2.y * nb.y +
-                          f3.x * nb.z + f3.y * nb.w;
-                    e[0] = __floats2bfloat162_rn(f0.x * winq, f0.y * winq);
-                    e[1] = __floats2bfloat162_rn(f1.x * winq, f1.y * winq);
-                    e[2] = __floats2bfloat162_rn(f2.x * winq, f2.y * winq);
-                    e[3] = __floats2bfloat162_rn(f3.x * winq, f3.y * winq);
-                    *reinterpret_cast<uint4 *>(rowp + pc * 16) = v;
+                    const float2 f0 = unpack_bf16(v[c].x), f1 = unpack_bf16(v[c].y);
+                    const float2 f2 = unpack_bf16(v[c].z), f3 = unpack_bf16(v[c].w);
+                    qn0 += f0.x * na.x + f0.y * na.y + f1.x * na.z + f1.y * na.w;
+                    qn1 += f2.x * nb.x + f2.y * nb.y + f3.x * nb.z + f3.y * nb.w;
+                    v[c].x = mul_bf16x2(v[c].x, w2); v[c].y = mul_bf16x2(v[c].y, w2);
+                    v[c].z = mul_bf16x2(v[c].z, w2); v[c].w = mul_bf16x2(v[c].w, w2);
                 }
-            }
-            s_qn[ph * LT + t] = qn;
-#pragma unroll 1
-            for (int q = 0; q < NBOX; ++q) {
-                unsigned char *rowp = smem + SM::K + q * SM::BOX + t * 128;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int pc = (c + t) & 7;
-                    uint4 v = *reinterpret_cast<uint4 *>(rowp + pc * 16);
-                    __nv_bfloat162 *e = reinterpret_cast<__nv_bfloat162 *>(&v);
-#pragma unroll
-                    for (int x = 0; x < 4; ++x) {
-                        float2 f = __bfloat1622float2(e[x]);
-                        e[x] = __floats2bfloat162_rn(f.x * w, f.y * w);
-                    }
-                    *reinterpret_cast<uint4 *>(rowp + pc * 16) = v;
-                }
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(rowp + (((c + t) & 7) << 4)) = v[c];
             }
+            // the epilogue of the previous tile has read its q . n (it arrives on HFREE afterwards)
+            if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
+            s_qn[t] = qn0 + qn1;
             fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor-core (async) proxy
-            mbar_arrive(&bars[B_SCALED]);
-            mbar_arrive(&bars[B_QNDONE]);
+            mbar_arrive(&bars[B_QSCALED]);
+            if (t == 0) TRACE(11);
         }
-    } else if (warp >= 12) {
-        // ================= normaliser update and C pass =================
-        const int r = tid - 384;                         // row within a 128-row half of C = TMEM lane
+    } else if (warp >= 12 && warp < 16) {
+        // ================= K~ = K * e^{u_t-x_last} in place; C pass =================
+        const int r = tid - 384;                         // K row / row within a 128-row half of C = TMEM lane
         const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
         const bool has_state = p.C0 != nullptr;
-        // ---- prologue: initial state -> TMEM (pre-scaled by the first decay) and Cb
+        // ---- prologue: initial state -> TMEM (pre-scaled by the first decay), Cb and n
         {
             const float decay0 = gbase[G_SCAL + 0];
             for (int hf = 0; hf < NHALF; ++hf) {
@@ -385,12 +402,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
 #pragma unroll
                     for (int x = 0; x < 32; x += 8) {
                         uint4 o;
-                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
-                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
-                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
-                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
-                        o.x = *reinterpret_cast<uint32_t *>(&a0); o.y = *reinterpret_cast<uint32_t *>(&a1);
-                        o.z = *reinterpret_cast<uint32_t *>(&a2); o.w = *reinterpret_cast<uint32_t *>(&a3);
+                        o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+                        o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                        o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+                        o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
                         const int c = c0 + x;
                         *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
                     }
@@ -408,73 +423,155 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
             const float *g = gbase + (size_t)k * GW;
-            const float decay = g[G_SCAL + 0];
+            const uint32_t w2 = pack_bf16(g[G_W + r], g[G_W + r]);
             const bool last = (k == NCH - 1);
             const float decay_next = last ? 1.0f : g[GW + G_SCAL + 0];
-            // n' = decay n + column sums of K~  (needs K~ complete, and q.n of this tile done reading n)
-            if (!(mbar_wait(&bars[B_SCALED], ph, abort_flag) && mbar_wait(&bars[B_QNDONE], ph, abort_flag))) break;
-            {
-                const int q = r >> 5, cp = r & 31;   // warp -> 64-column box, lane -> column pair
-                float a0 = 0.f, a1 = 0.f;
-                if (q < NBOX) {
-                    const unsigned char *box = smem + SM::K + q * SM::BOX;
-#pragma unroll 4
-                    for (int tt = 0; tt < LT; ++tt) {
-                        const uint32_t off = tt * 128 + ((((cp >> 2) ^ (tt & 7))) << 4) + ((cp & 3) << 2);
-                        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(box + off));
-                        a0 += f.x; a1 += f.y;
-                    }
-                    const int j = q * 64 + cp * 2;
-                    a0 += decay * s_n[j];
-                    a1 += decay * s_n[j + 1];
-                    s_n[j] = a0;
-                    s_n[j + 1] = a1;
-                    if (last && blockIdx.y == 0) { p.n1[(size_t)bh * DQK + j] = a0; p.n1[(size_t)bh * DQK + j + 1] = a1; }
+            if (!(mbar_wait(&bars[B_KFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
+            if (r == 0) TRACE(12);
+#pragma unroll 1
+            for (int q = 0; q < NBOX; ++q) {
+                unsigned char *rowp = smem + SM::K + q * SM::BOX + r * 128;
+                uint4 v[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(rowp + (((c + r) & 7) << 4));
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    v[c].x = mul_bf16x2(v[c].x, w2); v[c].y = mul_bf16x2(v[c].y, w2);
+                    v[c].z = mul_bf16x2(v[c].z, w2); v[c].w = mul_bf16x2(v[c].w, w2);
                 }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(rowp + (((c + r) & 7) << 4)) = v[c];
             }
-            mbar_arrive(&bars[B_NDONE]);  // K~ no longer read by this warpgroup
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[B_KSCALED]);
+            if (r == 0) TRACE(13);
             // C pass after the state update: refresh Cb (needs the read-out of this tile finished with the
             // old Cb), pre-scale C for the next tile; after the last tile write C out instead.
             if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
             tc_fence_after_sync();
+            if (r == 0) TRACE(14);
             for (int hf = 0; hf < NHALF; ++hf) {
                 const int j = hf * 128 + r;
 #pragma unroll 1
-                for (int c0 = 0; c0 < DVS; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(T_C + hf * 128 + lane_off + c0, v);
+                for (int c0 = 0; c0 < DVS; c0 += 64) {
+                    uint32_t va[32], vb[32];
+                    tmem_ld32(T_C + hf * 128 + lane_off + c0, va);
+                    tmem_ld32(T_C + hf * 128 + lane_off + c0 + 32, vb);
                     tmem_wait_ld();
                     if (last) {
                         float *dst = p.C1 + ((size_t)bh * DQK + j) * p.dv + col0 + c0;
 #pragma unroll
-                        for (int x = 0; x < 32; x += 4)
-                            *reinterpret_cast<float4 *>(dst + x) = make_float4(__uint_as_float(v[x]), __uint_as_float(v[x + 1]),
-                                                                                __uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                        for (int x = 0; x < 32; x += 4) {
+                            *reinterpret_cast<float4 *>(dst + x) = make_float4(__uint_as_float(va[x]), __uint_as_float(va[x + 1]),
+                                                                                __uint_as_float(va[x + 2]), __uint_as_float(va[x + 3]));
+                            *reinterpret_cast<float4 *>(dst + 32 + x) = make_float4(__uint_as_float(vb[x]), __uint_as_float(vb[x + 1]),
+                                                                                     __uint_as_float(vb[x + 2]), __uint_as_float(vb[x + 3]));
+                        }
                     } else {
 #pragma unroll
                         for (int x = 0; x < 32; x += 8) {
                             uint4 o;
-                            __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
-                            __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
-                            __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
-                            __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
-                            o.x = *reinterpret_cast<uint32_t *>(&a0); o.y = *reinterpret_cast<uint32_t *>(&a1);
-                            o.z = *reinterpret_cast<uint32_t *>(&a2); o.w = *reinterpret_cast<uint32_t *>(&a3);
-                            const int c = c0 + x;
+                            o.x = pack_bf16(__uint_as_float(va[x]), __uint_as_float(va[x + 1]));
+                            o.y = pack_bf16(__uint_as_float(va[x + 2]), __uint_as_float(va[x + 3]));
+                            o.z = pack_bf16(__uint_as_float(va[x + 4]), __uint_as_float(va[x + 5]));
+                            o.w = pack_bf16(__uint_as_float(va[x + 6]), __uint_as_float(va[x + 7]));
+                            int c = c0 + x;
+                            *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
+                            o.x = pack_bf16(__uint_as_float(vb[x]), __uint_as_float(vb[x + 1]));
+                            o.y = pack_bf16(__uint_as_float(vb[x + 2]), __uint_as_float(vb[x + 3]));
+                            o.z = pack_bf16(__uint_as_float(vb[x + 4]), __uint_as_float(vb[x + 5]));
+                            o.w = pack_bf16(__uint_as_float(vb[x + 6]), __uint_as_float(vb[x + 7]));
+                            c += 32;
                             *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
                         }
 #pragma unroll
-                        for (int x = 0; x < 32; ++x) v[x] = __float_as_uint(__uint_as_float(v[x]) * decay_next);
-                        tmem_st32(T_C + hf * 128 + lane_off + c0, v);
+                        for (int x = 0; x < 32; ++x) {
+                            va[x] = __float_as_uint(__uint_as_float(va[x]) * decay_next);
+                            vb[x] = __float_as_uint(__uint_as_float(vb[x]) * decay_next);
+                        }
+                        tmem_st32(T_C + hf * 128 + lane_off + c0, va);
+                        tmem_st32(T_C + hf * 128 + lane_off + c0 + 32, vb);
                     }
                 }
             }
+            if (r == 0) TRACE(15);
             if (!last) {
                 tmem_wait_st();
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
                 mbar_arrive(&bars[B_CBREADY]);
             }
+        }
+    } else if (warp >= 16) {
+        // ================= normaliser update n' = decay n + colsum(K~); H epilogue =================
+        const int r = tid - 512;                         // token row of H = TMEM lane
+        const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
+        __nv_bfloat16 *hrow = p.h + b * p.sh_b + hd * p.sh_h + col0;
+        for (int k = 0; k < NCH; ++k) {
+            const uint32_t ph = k & 1;
+            const float decay = gbase[(size_t)k * GW + G_SCAL + 0];
+            const bool last = (k == NCH - 1);
+            // K~ complete, and q . n of this tile has finished reading n
+            if (!(mbar_wait(&bars[B_KSCALED], ph, abort_flag) && mbar_wait(&bars[B_QSCALED], ph, abort_flag))) break;
+            {
+                const int q = r >> 5, cp = r & 31;   // warp -> 64-column box, lane -> column pair
+                if (q < NBOX) {
+                    const unsigned char *box = smem + SM::K + q * SM::BOX + ((cp & 3) << 2);
+                    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+                    for (int tt = 0; tt < LT; tt += 4) {
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const uint32_t off = (tt + x) * 128 + ((((cp >> 2) ^ ((tt + x) & 7))) << 4);
+                            const float2 f = unpack_bf16(*reinterpret_cast<const uint32_t *>(box + off));
+                            a0[x] += f.x; a1[x] += f.y;
+                        }
+                    }
+                    const int j = q * 64 + cp * 2;
+                    const float n0v = decay * s_n[j] + ((a0[0] + a0[1]) + (a0[2] + a0[3]));
+                    const float n1v = decay * s_n[j + 1] + ((a1[0] + a1[1]) + (a1[2] + a1[3]));
+                    s_n[j] = n0v;
+                    s_n[j + 1] = n1v;
+                    if (last && blockIdx.y == 0) { p.n1[(size_t)bh * DQK + j] = n0v; p.n1[(size_t)bh * DQK + j + 1] = n1v; }
+                }
+            }
+            mbar_arrive(&bars[B_NDONE]);  // K~ no longer read by the CUDA cores; n of this tile final
+            // epilogue: h = H / (max(|den|, e^{-m_t}) + eps)
+            if (!(mbar_wait(&bars[B_PREADY], ph, abort_flag) && mbar_wait(&bars[B_H2DONE], ph, abort_flag))) break;
+            tc_fence_after_sync();
+            if (r == 0) TRACE(7);
+            const float winq = __bfloat162float(__float2bfloat16_rn(gbase[(size_t)k * GW + G_WINQ + r]));  // the scale Q~ really carries
+            const float den = s_qn[r] * winq + s_rs[ph * LT + r];
+            const float inv = 1.0f / (fmaxf(fabsf(den), gbase[(size_t)k * GW + G_EMT + r]) + p.eps);
+            __nv_bfloat16 *hp = hrow + (int64_t)(k * LT + r) * p.sh_s;
+#pragma unroll 1
+            for (int c0 = 0; c0 < DVS; c0 += 64) {
+                uint32_t va[32], vb[32];
+                tmem_ld32(T_H + lane_off + c0, va);
+                tmem_ld32(T_H + lane_off + c0 + 32, vb);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 o;
+                    o.x = pack_bf16(__uint_as_float(va[j]) * inv, __uint_as_float(va[j + 1]) * inv);
+                    o.y = pack_bf16(__uint_as_float(va[j + 2]) * inv, __uint_as_float(va[j + 3]) * inv);
+                    o.z = pack_bf16(__uint_as_float(va[j + 4]) * inv, __uint_as_float(va[j + 5]) * inv);
+                    o.w = pack_bf16(__uint_as_float(va[j + 6]) * inv, __uint_as_float(va[j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(hp + c0 + j) = o;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 o;
+                    o.x = pack_bf16(__uint_as_float(vb[j]) * inv, __uint_as_float(vb[j + 1]) * inv);
+                    o.y = pack_bf16(__uint_as_float(vb[j + 2]) * inv, __uint_as_float(vb[j + 3]) * inv);
+                    o.z = pack_bf16(__uint_as_float(vb[j + 4]) * inv, __uint_as_float(vb[j + 5]) * inv);
+                    o.w = pack_bf16(__uint_as_float(vb[j + 6]) * inv, __uint_as_float(vb[j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(hp + c0 + 32 + j) = o;
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&bars[B_HFREE]);
+            if (r == 0) TRACE(8);
         }
     }
 
@@ -572,3 +669,9 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
 }
 
 }  // namespace xl
+
+#ifdef XL_TC_TRACE
+extern "C" int xlstm_debug_trace(long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, xl::g_trace, sizeof(long long) * 64 * 32);
+}
+#endif

@@ -1,0 +1,72 @@
+"""Sharding of the hot path over the GPUs of one box (one process per GPU, torch.distributed).
+
+mLSTM heads are independent (no cross-head term in the cell), so a layer shards by heads: rank r
+owns heads ``[r*NH/G, (r+1)*NH/G)`` - its column slices of the q/k/v/gate projections and its
+heads' (C, n, m) - and ONE all-gather of h precedes the replicated out-projection.  Decode batches
+and the sLSTM stack shard by batch with no collective at all.  The backend is NCCL on GPUs and
+gloo in the CPU tests; remote data always lands in local memory through the collective before
+any kernel reads it.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def head_range(num_heads: int, world: int, rank: int) -> Tuple[int, int]:
+    """Heads owned by ``rank``; ``num_heads`` must divide evenly (NH = 8 gives G in 1, 2, 4, 8)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    if num_heads % world:
+        raise ValueError(f"{num_heads} heads do not shard over {world} ranks")
+    per = num_heads // world
+    return rank * per, (rank + 1) * per
+
+
+def batch_range(batch: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous batch rows owned by ``rank`` (sizes differ by at most one row)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    base, extra = divmod(batch, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def shard_heads(t: torch.Tensor, world: int, rank: int, dim: int = 1) -> torch.Tensor:
+    """Slice of a ``[B, NH, ...]`` tensor (or a state tensor) holding this rank's heads."""
+    lo, hi = head_range(t.shape[dim], world, rank)
+    return t.narrow(dim, lo, hi - lo)
+
+
+def all_gather_heads(h_local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """``[B, NH/G, S, dv]`` on every rank -> ``[B, NH, S, dv]`` on every rank, one collective."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return h_local
+    h_local = h_local.contiguous()
+    B, nh, S, dv = h_local.shape
+    gathered = torch.empty((world * B, nh, S, dv), dtype=h_local.dtype, device=h_local.device)  # rank-major
+    dist.all_gather_into_tensor(gathered, h_local, group=group)
+    return gathered.view(world, B, nh, S, dv).permute(1, 0, 2, 3, 4).reshape(B, world * nh, S, dv)
+
+
+def head_sharded_prefill(cell: Callable, q, k, v, i, f, state=None, out_proj: Optional[torch.Tensor] = None,
+                         group: Optional[dist.ProcessGroup] = None):
+    """Run ``cell(q, k, v, i, f, state) -> (h, state)`` on this rank's heads, all-gather h, and apply
+    the replicated out-projection ``[NH*dv, D]`` if given.  Inputs are the FULL tensors; each rank
+    slices its heads.  Returns ``(y or h_full, local_state)``."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    sl = lambda t: shard_heads(t, world, rank)
+    st = None if state is None else tuple(sl(s) for s in state)
+    h_local, st_local = cell(sl(q), sl(k), sl(v), sl(i), sl(f), st)
+    h = all_gather_heads(h_local, group)
+    if out_proj is None:
+        return h, st_local
+    B, NH, S, dv = h.shape
+    return h.permute(0, 2, 1, 3).reshape(B, S, NH * dv) @ out_proj, st_local
+
+
+__all__ = ["head_range", "batch_range", "shard_heads", "all_gather_heads", "head_sharded_prefill"]
