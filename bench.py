@@ -334,6 +334,12 @@ def run_ours(args):
     }
     if prefill is not None:
         line["prefill"] = prefill
+    if not args.no_extras:
+        line["slstm"] = run_slstm(torch, dist, device, world, rank)
+        if rank == 0:
+            line["softcap"] = run_softcap(torch, ops, device)
+            if not args.no_model:
+                line["model"] = run_model(torch, device, 2048, 256)
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
         print(json.dumps(line), flush=True)
@@ -408,6 +414,110 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
                          "flop_count": "4*dqk*dv + L*(dqk+dv) per token per head (causal half)", "peak_source": which}}
 
 
+def _time_cuda(torch, fn, reps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_softcap(torch, ops, device):
+    """Logit soft-cap at the prefill shape of BASELINE configs[2]: [2048, 50304] fp32 (412 MB > L2)."""
+    x = torch.randn(2048, 50304, device=device) * 20
+    y = torch.empty_like(x)
+    ops.softcap(x, 30.0, out=y)
+    ms = _time_cuda(torch, lambda: ops.softcap(x, 30.0, out=y), 5)
+    hbm, _, which = peaks()
+    gbs = 2 * x.numel() * 4 / (ms * 1e-3) / 1e9
+    return {"workload": "softcap [2048,50304] fp32 cap=30", "ms": ms,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_source": which}}
+
+
+def run_slstm(torch, dist, device, world, rank):
+    """BASELINE configs[4]: 4 sLSTM blocks with block-diagonal recurrent weights, d=1024, 4 heads x 256,
+    B=32 (sharded over the ranks), S=1024, bf16 activations, fp32 state."""
+    from xlstm_cuda.blocks import sLSTMBlockDiag
+
+    class Cfg:
+        inp_dim, head_dim, head_num, p_factor, norm_eps, gate_soft_cap = 1024, 256, 4, (2.0, 4 / 3), 1e-6, 15.0
+
+    Bs, S = max(1, 32 // world), 1024
+    torch.manual_seed(4 + rank)
+    blocks = [sLSTMBlockDiag(Cfg()).to(device) for _ in range(4)]
+    with torch.no_grad():
+        for blk in blocks:
+            for lin in (blk.R_i, blk.R_f, blk.R_z, blk.R_o):
+                for b in lin.blocks:
+                    b.weight.normal_(0.0, 0.02)
+            blk.W_f.bias.copy_(torch.linspace(3.0, 6.0, 1024))
+            blk.to(torch.bfloat16)
+    x = torch.randn(Bs, S, 1024, device=device).to(torch.bfloat16)
+
+    def fwd():
+        with torch.inference_mode():
+            y = x
+            for blk in blocks:
+                y, _ = blk(y)
+        return y
+
+    fwd()
+    ms = _time_cuda(torch, fwd, 3)
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    return {"workload": "4 sLSTM blocks (block-diagonal R), d=1024, 4x256, B=32, S=1024, bf16 (BASELINE configs[4])",
+            "parallelism": f"batch-sharded x{world}", "scaling": "strong", "ms": ms,
+            "tokens_per_s": Bs * world * S / (ms * 1e-3), "us_per_step_per_block": ms * 1e3 / (4 * S),
+            "bound": "latency (sequential through h_{t-1}); includes the input-side GEMMs, norms and FFN of each block"}
+
+
+def run_model(torch, device, prompt_len, new_tokens):
+    """BASELINE configs[2]: xLSTM-7B-shaped random-init model, prefill then greedy decode, B=1."""
+    import tempfile
+    from xlstm_cuda.generate import xLSTMRunner
+    from xlstm_cuda.utils import XLSTM_7B_CONFIG, write_model_dir
+    with tempfile.TemporaryDirectory() as tmp:
+        d = write_model_dir(tmp, dict(XLSTM_7B_CONFIG))
+        runner = xLSTMRunner(str(d), device=device)
+    with torch.no_grad():
+        for name, prm in runner.model.named_parameters():
+            if prm.dim() >= 2:
+                prm.normal_(0.0, 0.02)
+            elif name.endswith("fgate_proj.bias"):
+                prm.copy_(torch.linspace(3.0, 6.0, prm.numel()))
+            elif name.endswith("bias"):
+                prm.zero_()
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 50304, (1, prompt_len), generator=g)
+    runner.forward(ids[:, :256])  # warm-up (kernels, cuBLAS handles)
+    runner.reset_state()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    torch.cuda.synchronize()
+    e[0].record()
+    logits = runner.forward(ids)
+    tok = int(logits[0, -1].argmax())
+    e[1].record()
+    out = []
+    for _ in range(new_tokens):
+        out.append(tok)
+        tok = runner.generate_next_token(torch.tensor([[tok]]), temperature=0.0)
+    e[2].record()
+    torch.cuda.synchronize()
+    pre_ms, dec_ms = e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+    n_params = sum(p.numel() for p in runner.model.parameters())
+    del runner
+    torch.cuda.empty_cache()
+    return {"workload": f"xLSTM-7B-shaped random init, B=1, prompt {prompt_len} + {new_tokens} greedy tokens, bf16 (BASELINE configs[2])",
+            "params": n_params, "prefill_ms": pre_ms, "prefill_tokens_per_s": prompt_len / (pre_ms * 1e-3),
+            "decode_ms_per_token": dec_ms / new_tokens, "decode_tokens_per_s": new_tokens / (dec_ms * 1e-3),
+            "note": "GEMM-bound context number (cuBLAS via torch); the mLSTM cell is ~1 % of prefill FLOPs"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -418,6 +528,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--prefill-seq", type=int, default=32768)
     ap.add_argument("--prefill-reps", type=int, default=3)
+    ap.add_argument("--no-extras", action="store_true", help="skip the soft-cap, sLSTM and full-model sub-benchmarks")
+    ap.add_argument("--no-model", action="store_true", help="skip the 7B-shaped full-model run")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -108,7 +108,10 @@ slstm_scan_kernel(const T *__restrict__ z, const T *__restrict__ ig, const T *__
 // (2) block-diagonal recurrent sLSTM, recurrent weights resident in shared memory
 // ---------------------------------------------------------------------------
 constexpr int REC_THREADS = 256;
-constexpr int REC_BG = 8;  // batch rows per cluster
+#ifndef XL_REC_BG
+#define XL_REC_BG 8
+#endif
+constexpr int REC_BG = XL_REC_BG;  // batch rows per cluster
 
 template <typename T> struct RStore;     // how R sits in shared memory
 template <> struct RStore<float> {
