@@ -109,7 +109,7 @@ slstm_scan_kernel(const T *__restrict__ z, const T *__restrict__ ig, const T *__
 // ---------------------------------------------------------------------------
 constexpr int REC_THREADS = 256;
 #ifndef XL_REC_BG
-#define XL_REC_BG 8
+#define XL_REC_BG 4
 #endif
 constexpr int REC_BG = XL_REC_BG;  // batch rows per cluster
 

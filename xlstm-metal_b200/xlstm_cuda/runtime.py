@@ -69,6 +69,28 @@ class DecodePipeline:
             self.ev_out[s].record(self.s_out)
         self.t += 1
 
+    def capture(self, steps) -> torch.cuda.CUDAGraph:
+        """Record a sequence of ``step`` calls - each ``(packed_host, state_in, state_out, h_host)`` -
+        into one CUDA graph: the copies and kernels keep their three-stream overlap as parallel
+        branches of the graph, and a replay costs one launch instead of ~10 Python-side calls per
+        step.  The producer refills the SAME pinned buffers between replays.  Replay on any stream
+        with ``graph.replay()``."""
+        graph = torch.cuda.CUDAGraph()
+        self.t = 0
+        with torch.cuda.graph(graph, stream=self.s_run, capture_error_mode="relaxed"):
+            fork = torch.cuda.Event()
+            fork.record(self.s_run)
+            self.s_in.wait_event(fork)
+            self.s_out.wait_event(fork)
+            for packed_host, state_in, state_out, h_host in steps:
+                self.step(packed_host, state_in, state_out, h_host)
+            for side in (self.s_in, self.s_out):
+                join = torch.cuda.Event()
+                join.record(side)
+                self.s_run.wait_event(join)
+        self.t = 0
+        return graph
+
     def streams(self) -> List[torch.cuda.Stream]:
         return [self.s_in, self.s_run, self.s_out]
 
