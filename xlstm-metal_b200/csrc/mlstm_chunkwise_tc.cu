@@ -19,9 +19,15 @@
 // them to caller-provided scratch.
 //
 // Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc),
-// warps 4-7 gate matrix P and the denominators, warps 8-11 Q~ scaling and q.n,
-// warps 12-15 K~ scaling and the C pass (rescale C in TMEM, refresh Cb),
-// warps 16-19 normaliser update and the H epilogue.
+// warps 4-7 gate matrix P, then the C pass for rows [128,256) of C;
+// warps 8-11 Q~ scaling and q.n for the first half of the dqk boxes;
+// warps 12-15 K~ scaling, then the C pass for rows [0,128) (refresh Cb);
+// warps 16-19 Q~ for the other boxes, normaliser update, H epilogue.
+// MMA issue order per tile: S, state update, P V, read-out (the update only needs the short K~
+// pass and frees K for the next tile's load while the longer Q~ pass still runs).
+// C is held in TMEM as C~ = C e^{-rho}: rho absorbs the per-tile decay, so the accumulator is not
+// rescaled every tile (TMEM load/store bandwidth, ~64 B/clk/SM, is the scarce resource); it is
+// multiplied once whenever -rho would pass 30.
 // TMEM columns: C [0,256)  S/P [256,384)  H [384,512).
 // Every mbarrier wait is bounded; a time-out sets the status word in the
 // scratch buffer, releases all roles and frees TMEM before the CTA returns.
@@ -62,73 +68,119 @@ struct TcParams {
 };
 
 // ---------------------------------------------------------------------------
-// gate pre-pass: one warp per (batch, head), sequential over tiles of 128 tokens
+// gate pre-pass: one CTA per (batch, head).  Only the stabiliser m couples the tiles, and
+// only through two numbers per tile (G = sum of log-sigmoid f, U = max of u = i - b), so:
+//   phase 1  all warps, tiles in parallel: G_c, U_c              -> shared memory
+//   phase 2  one thread: m_{c+1} = G_c + max(m_c, U_c)           (NCH scalar steps)
+//   phase 3  all warps, tiles in parallel: the per-token scalars -> scratch
+// Sums and maxima are kept in double so that differences of large cumulative sums stay exact.
 // ---------------------------------------------------------------------------
+constexpr int GP_THREADS = 256;
+constexpr double RESCALE_AT = 30.0;   // rescale C~ when the frame exponent would exceed e^30
+
 template <typename T>
-__global__ void __launch_bounds__(32)
+__device__ __forceinline__ void gate_tile_scan(const T *ip, const T *fp, int64_t sg_s, int c, int lane, double (&bcum)[4],
+                                               double (&u)[4], double (&pmax)[4], double &excl_max, double &G,
+                                               double &U) {
+    const int t0 = c * LT + lane * 4;
+    float iv[4];
+    double run = 0.0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        iv[e] = Elem<T>::ld(ip + (int64_t)(t0 + e) * sg_s);
+        run += (double)logsigmoid(Elem<T>::ld(fp + (int64_t)(t0 + e) * sg_s));
+        bcum[e] = run;
+    }
+    double incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    const double off = incl - run;
+    double pm = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        bcum[e] += off;
+        u[e] = (double)iv[e] - bcum[e];
+        pm = fmax(pm, u[e]);
+        pmax[e] = pm;
+    }
+    double mincl = pm;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double v = __shfl_up_sync(0xffffffffu, mincl, o);
+        if (lane >= o) mincl = fmax(mincl, v);
+    }
+    excl_max = __shfl_up_sync(0xffffffffu, mincl, 1);
+    if (lane == 0) excl_max = -INFINITY;
+    U = __shfl_sync(0xffffffffu, mincl, 31);
+    G = __shfl_sync(0xffffffffu, bcum[3], 31);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(GP_THREADS)
 mlstm_gate_prep_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64_t sg_b, int64_t sg_h, int64_t sg_s,
                        const float *__restrict__ m0, float *__restrict__ gates, float *__restrict__ m_out, int NH,
                        int NCH, float qscale) {
-    const int bh = blockIdx.x, b = bh / NH, hd = bh % NH, lane = threadIdx.x;
+    extern __shared__ double s_gp[];   // [NCH] each: G, U (-> m before the tile), rho before the tile, C multiplier
+    double *sG = s_gp, *sU = s_gp + NCH, *sRho = s_gp + 2 * NCH, *sMul = s_gp + 3 * NCH;
+    const int bh = blockIdx.x, b = bh / NH, hd = bh % NH;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = GP_THREADS / 32;
     const T *ip = ig + b * sg_b + hd * sg_h;
     const T *fp = fg + b * sg_b + hd * sg_h;
-    double m = m0 ? (double)m0[bh] : 0.0;
-    for (int c = 0; c < NCH; ++c) {
-        const int t0 = c * LT + lane * 4;
-        double bcum[4], u[4], x[4];
-        float iv[4];
-        double run = 0.0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            iv[e] = Elem<T>::ld(ip + (int64_t)(t0 + e) * sg_s);
-            run += (double)logsigmoid(Elem<T>::ld(fp + (int64_t)(t0 + e) * sg_s));
-            bcum[e] = run;
-        }
-        // exclusive warp scan of the lane totals
-        double incl = run;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const double v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-        }
-        const double off = incl - run;
-        double pm = -INFINITY;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            bcum[e] += off;
-            u[e] = (double)iv[e] - bcum[e];
-            pm = fmax(pm, u[e]);
-            x[e] = pm;
-        }
-        double mincl = pm;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const double v = __shfl_up_sync(0xffffffffu, mincl, o);
-            if (lane >= o) mincl = fmax(mincl, v);
-        }
-        double carry = __shfl_up_sync(0xffffffffu, mincl, 1);
-        if (lane == 0) carry = -INFINITY;
-        carry = fmax(carry, m);
-        const double x_last = fmax(__shfl_sync(0xffffffffu, mincl, 31), m);
-        const double G = __shfl_sync(0xffffffffu, bcum[3], 31);
-        float *g = gates + ((size_t)bh * NCH + c) * GW;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int t = lane * 4 + e;
-            const double xt = fmax(x[e], carry);
-            g[G_U2 + t] = (float)(u[e] * (double)LOG2E);
-            g[G_X2 + t] = (float)(xt * (double)LOG2E);
-            g[G_WINQ + t] = expf((float)(m - xt)) * qscale;
-            g[G_W + t] = expf((float)(u[e] - x_last));
-            g[G_EMT + t] = expf(-(float)(bcum[e] + xt));
-        }
-        if (lane == 0) {
-            g[G_SCAL + 0] = expf((float)(m - x_last));  // decay applied to the carried state
-            g[G_SCAL + 1] = (float)(G + x_last);        // stabiliser after this tile
-        }
-        m = G + x_last;
+    double bcum[4], u[4], pmax[4], excl, G, U;
+    for (int c = warp; c < NCH; c += nwarp) {
+        gate_tile_scan<T>(ip, fp, sg_s, c, lane, bcum, u, pmax, excl, G, U);
+        if (lane == 0) { sG[c] = G; sU[c] = U; }
     }
-    if (lane == 0) m_out[bh] = (float)m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // C is kept in TMEM as C~ = C e^{-rho}: rho absorbs the per-tile decay so that the accumulator is
+        // NOT rescaled every tile; only when -rho would exceed RESCALE_AT is C~ multiplied once (sMul).
+        double m = m0 ? (double)m0[bh] : 0.0, rho = 0.0;
+        for (int c = 0; c < NCH; ++c) {
+            const double x_last = fmax(m, sU[c]);
+            const double logdec = m - x_last;           // log of the decay applied to the carried state, <= 0
+            sRho[c] = rho;
+            if (rho + logdec < -RESCALE_AT) { sMul[c] = exp(rho + logdec); rho = 0.0; }
+            else { sMul[c] = 1.0; rho += logdec; }
+            const double mn = sG[c] + x_last;
+            sU[c] = m;   // stabiliser carried INTO tile c
+            sG[c] = rho; // frame of the state AFTER tile c's update (G itself is recomputed in phase 3)
+            m = mn;
+        }
+        m_out[bh] = (float)m;
+    }
+    __syncthreads();
+    for (int c = warp; c < NCH; c += nwarp) {
+        gate_tile_scan<T>(ip, fp, sg_s, c, lane, bcum, u, pmax, excl, G, U);
+        const double m = sU[c], rho_in = sRho[c], rho_out = sG[c];
+        const double x_last = fmax(U, m);
+        const double carry = fmax(excl, m);
+        float *g = gates + ((size_t)bh * NCH + c) * GW;
+        float4 o_u2, o_x2, o_wq, o_w, o_em;
+        float *pu = &o_u2.x, *px = &o_x2.x, *pq = &o_wq.x, *pw = &o_w.x, *pe = &o_em.x;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const double xt = fmax(pmax[e], carry);
+            pu[e] = (float)(u[e] * (double)LOG2E);
+            px[e] = (float)(xt * (double)LOG2E);
+            pq[e] = expf((float)(m - xt + rho_in)) * qscale;   // read-out sees C~ = C e^{-rho_in}
+            pw[e] = expf((float)(u[e] - x_last - rho_out));     // new tokens enter the frame after the update
+            pe[e] = expf(-(float)(bcum[e] + xt));
+        }
+        *reinterpret_cast<float4 *>(g + G_U2 + lane * 4) = o_u2;
+        *reinterpret_cast<float4 *>(g + G_X2 + lane * 4) = o_x2;
+        *reinterpret_cast<float4 *>(g + G_WINQ + lane * 4) = o_wq;
+        *reinterpret_cast<float4 *>(g + G_W + lane * 4) = o_w;
+        *reinterpret_cast<float4 *>(g + G_EMT + lane * 4) = o_em;
+        if (lane == 0) {
+            g[G_SCAL + 0] = (float)sMul[c];             // multiplier for C~ and n~ before this tile (1 = leave alone)
+            g[G_SCAL + 1] = (float)(G + x_last);        // stabiliser after this tile
+            g[G_SCAL + 2] = expf((float)rho_out);       // C = C~ * this after the tile (used for the final state)
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -152,7 +204,7 @@ template <int DQK> struct Smem {
 };
 
 enum { B_QFULL = 0, B_KFULL, B_VFULL, B_SDONE, B_H1DONE, B_UPDDONE, B_H2DONE, B_QSCALED, B_KSCALED, B_CBREADY,
-       B_PREADY, B_HFREE, B_NDONE, B_NBARS };
+       B_PREADY, B_HFREE, B_NDONE, B_KREAD, B_NBARS };
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -163,13 +215,152 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&v);
 }
-// packed bf16 x bf16 -> bf16 (one rounding); `w2` holds the same bf16 scale in both halves
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t w2) {
-    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&w2));
-    return *reinterpret_cast<uint32_t *>(&r);
-}
 __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
     return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+
+// Q~ = Q * rowscale in place for boxes [q_begin, q_end) of the Q tile, and the partial q . n of those
+// columns added to s_qn.  Lane mapping: lane = (g, c) with c the physical 16-byte chunk and g a row
+// group; a warp owns the rows with (row & 7) in {2w, 2w+1}, so for a fixed residue rho every lane
+// always meets the same LOGICAL chunk c ^ rho: its 8 values of n stay in registers for 4 rows and the
+// tile loads are 4 x 128 contiguous bytes per instruction (no bank conflicts).
+template <int DQK, int QB, int QE>
+__device__ __forceinline__ void q_pass_boxes(unsigned char *smem, const float *s_n, float *s_qn, const float (&w2)[2][4],
+                                             int wl, int lane) {
+    using SM = Smem<DQK>;
+    const int c = lane & 7, g = lane >> 3;
+    float part[2][4];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int rho = 2 * wl + rr;
+        const int row0 = rho + 8 * g;                 // rows row0 + 32 i
+#pragma unroll
+        for (int i = 0; i < 4; ++i) part[rr][i] = 0.f;
+#pragma unroll
+        for (int q = QB; q < QE; ++q) {
+            const float *np = s_n + q * 64 + ((c ^ rho) << 3);
+            const float4 na = *reinterpret_cast<const float4 *>(np);
+            const float4 nb = *reinterpret_cast<const float4 *>(np + 4);
+            unsigned char *base = smem + SM::Q + q * SM::BOX + row0 * 128 + (c << 4);
+            uint4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = *reinterpret_cast<const uint4 *>(base + i * 32 * 128);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y);
+                const float2 f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+                part[rr][i] += (f0.x * na.x + f0.y * na.y + f1.x * na.z + f1.y * na.w) +
+                               (f2.x * nb.x + f2.y * nb.y + f3.x * nb.z + f3.y * nb.w);
+                const float w = w2[rr][i];   // fp32 scale, one rounding of the product
+                v[i].x = pack_bf16(f0.x * w, f0.y * w); v[i].y = pack_bf16(f1.x * w, f1.y * w);
+                v[i].z = pack_bf16(f2.x * w, f2.y * w); v[i].w = pack_bf16(f3.x * w, f3.y * w);
+                *reinterpret_cast<uint4 *>(base + i * 32 * 128) = v[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float v = part[rr][i];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            if (c == 0) atomicAdd(s_qn + (2 * wl + rr) + 8 * g + 32 * i, v);
+        }
+}
+
+// the row scales of the 8 rows a lane of the Q~ pass owns
+__device__ __forceinline__ void q_pass_scales(const float *winq_g, int wl, int lane, float (&w2)[2][4]) {
+    const int g = lane >> 3;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            w2[rr][i] = winq_g[(2 * wl + rr) + 8 * g + 32 * i];
+        }
+}
+
+// One 128-row half of the initial state: global fp32 -> Cb (bf16, swizzled MN-major) and TMEM
+// (pre-scaled by the first tile's decay).  `src` is this thread's row (NULL = zero state).
+template <int DQK>
+__device__ __forceinline__ void c_init_half(unsigned char *smem, uint32_t t_half, const float *src, int j, float decay0) {
+    using SM = Smem<DQK>;
+#pragma unroll 1
+    for (int c0 = 0; c0 < DVS; c0 += 32) {
+        uint32_t v[32];
+#pragma unroll
+        for (int x = 0; x < 32; x += 4) {
+            float4 f = src ? *reinterpret_cast<const float4 *>(src + c0 + x) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[x] = __float_as_uint(f.x); v[x + 1] = __float_as_uint(f.y);
+            v[x + 2] = __float_as_uint(f.z); v[x + 3] = __float_as_uint(f.w);
+        }
+#pragma unroll
+        for (int x = 0; x < 32; x += 8) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+            o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+            o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+            o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
+            const int c = c0 + x;
+            *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
+        }
+#pragma unroll
+        for (int x = 0; x < 32; ++x) v[x] = __float_as_uint(__uint_as_float(v[x]) * decay0);
+        tmem_st32(t_half + c0, v);
+    }
+}
+
+// C pass for one 128-row half after the state update: TMEM -> Cb (bf16) and back to TMEM scaled by
+// the next tile's decay; after the last tile the fp32 rows go to `dst` instead.
+template <int DQK>
+__device__ __forceinline__ void c_pass_half(unsigned char *smem, uint32_t t_half, int j, bool last, float decay_next,
+                                            float *dst) {
+    using SM = Smem<DQK>;
+#pragma unroll 1
+    for (int c0 = 0; c0 < DVS; c0 += 64) {
+        uint32_t va[32], vb[32];
+        tmem_ld32(t_half + c0, va);
+        tmem_ld32(t_half + c0 + 32, vb);
+        tmem_wait_ld();
+        if (last) {   // decay_next carries the frame factor e^{rho}: C = C~ e^{rho}
+#pragma unroll
+            for (int x = 0; x < 32; x += 4) {
+                *reinterpret_cast<float4 *>(dst + c0 + x) =
+                    make_float4(__uint_as_float(va[x]) * decay_next, __uint_as_float(va[x + 1]) * decay_next,
+                                __uint_as_float(va[x + 2]) * decay_next, __uint_as_float(va[x + 3]) * decay_next);
+                *reinterpret_cast<float4 *>(dst + c0 + 32 + x) =
+                    make_float4(__uint_as_float(vb[x]) * decay_next, __uint_as_float(vb[x + 1]) * decay_next,
+                                __uint_as_float(vb[x + 2]) * decay_next, __uint_as_float(vb[x + 3]) * decay_next);
+            }
+        } else {
+#pragma unroll
+            for (int x = 0; x < 32; x += 8) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(va[x]), __uint_as_float(va[x + 1]));
+                o.y = pack_bf16(__uint_as_float(va[x + 2]), __uint_as_float(va[x + 3]));
+                o.z = pack_bf16(__uint_as_float(va[x + 4]), __uint_as_float(va[x + 5]));
+                o.w = pack_bf16(__uint_as_float(va[x + 6]), __uint_as_float(va[x + 7]));
+                int c = c0 + x;
+                *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
+                o.x = pack_bf16(__uint_as_float(vb[x]), __uint_as_float(vb[x + 1]));
+                o.y = pack_bf16(__uint_as_float(vb[x + 2]), __uint_as_float(vb[x + 3]));
+                o.z = pack_bf16(__uint_as_float(vb[x + 4]), __uint_as_float(vb[x + 5]));
+                o.w = pack_bf16(__uint_as_float(vb[x + 6]), __uint_as_float(vb[x + 7]));
+                c += 32;
+                *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
+            }
+            if (decay_next != 1.0f) {   // CTA-uniform: a rescale tile (rare); otherwise C~ stays as it is
+#pragma unroll
+                for (int x = 0; x < 32; ++x) {
+                    va[x] = __float_as_uint(__uint_as_float(va[x]) * decay_next);
+                    vb[x] = __float_as_uint(__uint_as_float(vb[x]) * decay_next);
+                }
+                tmem_st32(t_half + c0, va);
+                tmem_st32(t_half + c0 + 32, vb);
+            }
+        }
+    }
 }
 
 template <int DQK>
@@ -196,11 +387,12 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         mbar_init(&bars[B_QFULL], 1);   mbar_init(&bars[B_KFULL], 1);   mbar_init(&bars[B_VFULL], 1);
         mbar_init(&bars[B_SDONE], 1);   mbar_init(&bars[B_H1DONE], 1);  mbar_init(&bars[B_UPDDONE], 1);
         mbar_init(&bars[B_H2DONE], 1);
-        mbar_init(&bars[B_QSCALED], 128); mbar_init(&bars[B_KSCALED], 128); mbar_init(&bars[B_CBREADY], 128);
-        mbar_init(&bars[B_PREADY], 128);  mbar_init(&bars[B_HFREE], 128);   mbar_init(&bars[B_NDONE], 128);
+        mbar_init(&bars[B_QSCALED], 256); mbar_init(&bars[B_KSCALED], 128); mbar_init(&bars[B_CBREADY], 128 * NHALF);
+        mbar_init(&bars[B_PREADY], 128);  mbar_init(&bars[B_HFREE], 128);   mbar_init(&bars[B_NDONE], 128);  mbar_init(&bars[B_KREAD], 128);
         mbar_fence_init();
         tma_prefetch_desc(&p.tq); tma_prefetch_desc(&p.tk); tma_prefetch_desc(&p.tv);
     }
+    if (tid < LT) s_qn[tid] = 0.f;   // q . n is accumulated with shared-memory atomics by two warpgroups
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     tc_fence_before_sync();
     __syncthreads();
@@ -216,12 +408,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         if (lane == 0) {
             for (int k = 0; k < NCH; ++k) {
                 const int t0 = k * LT;
-                if (k > 0 && !mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag)) break;
-                TRACE(16);
-                mbar_expect_tx(&bars[B_QFULL], NBOX * SM::BOX);
-                for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[B_QFULL], q * 64, t0, hd, b);
                 if (k > 0 && !(mbar_wait(&bars[B_UPDDONE], (k - 1) & 1, abort_flag) &&
-                               mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
+                               mbar_wait(&bars[B_KREAD], (k - 1) & 1, abort_flag))) break;
                 TRACE(17);
                 mbar_expect_tx(&bars[B_KFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::K + q * SM::BOX, &p.tk, &bars[B_KFULL], q * 64, t0, hd, b);
@@ -229,6 +417,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 TRACE(18);
                 mbar_expect_tx(&bars[B_VFULL], 2 * SM::BOX);
                 for (int q = 0; q < 2; ++q) tma_load_4d(smem + SM::V + q * SM::BOX, &p.tv, &bars[B_VFULL], col0 + q * 64, t0, hd, b);
+                if (k > 0 && !mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag)) break;
+                TRACE(16);
+                mbar_expect_tx(&bars[B_QFULL], NBOX * SM::BOX);
+                for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[B_QFULL], q * 64, t0, hd, b);
             }
         }
     } else if (warp == 1) {
@@ -256,19 +448,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                     mma_ss(T_S, dQ + o, dK + o, ID_KK, kk > 0);
                 }
                 mma_commit(&bars[B_SDONE]);
-                // H = Q~ Cb   (Q~ scaled in place; Cb and the pre-scaled C from the previous C pass)
-                if (!(mbar_wait(&bars[B_QSCALED], ph, abort_flag) && mbar_wait(&bars[B_CBREADY], ph, abort_flag))) break;
-                if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
-                tc_fence_after_sync();
-                TRACE(2);
-#pragma unroll
-                for (int kk = 0; kk < DQK / 16; ++kk) {
-                    const uint32_t o = ((kk >> 2) * SM::BOX + (kk & 3) * 32) >> 4;
-                    mma_ss(T_H, dQ + o, dCb + kk * (2048 >> 4), ID_KM, kk > 0);
-                }
-                mma_commit(&bars[B_H1DONE]);
-                // C += K~^T V
-                if (!(mbar_wait(&bars[B_KSCALED], ph, abort_flag) && mbar_wait(&bars[B_VFULL], ph, abort_flag))) break;
+                // C += K~^T V first: it only needs K~ (a short pass) and frees K for the next tile's load,
+                // which then overlaps the longer Q~ pass.  C was pre-scaled by the previous C pass.
+                if (!(mbar_wait(&bars[B_KSCALED], ph, abort_flag) && mbar_wait(&bars[B_VFULL], ph, abort_flag) &&
+                      mbar_wait(&bars[B_CBREADY], ph, abort_flag))) break;
                 tc_fence_after_sync();
                 TRACE(3);
 #pragma unroll
@@ -277,13 +460,24 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                     for (int kk = 0; kk < LT / 16; ++kk)
                         mma_ss(T_C + hf * 128, dKm + ((hf * 2 * SM::BOX + kk * 2048) >> 4), dV + kk * (2048 >> 4), ID_MM, true);
                 mma_commit(&bars[B_UPDDONE]);
-                // H += P V
+                // H = P V  (first write of H for this tile: the previous epilogue must have drained it)
                 if (!mbar_wait(&bars[B_PREADY], ph, abort_flag)) break;
+                if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
                 tc_fence_after_sync();
                 TRACE(4);
 #pragma unroll
-                for (int kk = 0; kk < LT / 16; ++kk) mma_ts(T_H, T_S + kk * 8, dV + kk * (2048 >> 4), ID_KM, true);
+                for (int kk = 0; kk < LT / 16; ++kk) mma_ts(T_H, T_S + kk * 8, dV + kk * (2048 >> 4), ID_KM, kk > 0);
                 mma_commit(&bars[B_H2DONE]);
+                // H += Q~ Cb   (Q~ scaled in place; Cb from the previous C pass)
+                if (!mbar_wait(&bars[B_QSCALED], ph, abort_flag)) break;
+                tc_fence_after_sync();
+                TRACE(2);
+#pragma unroll
+                for (int kk = 0; kk < DQK / 16; ++kk) {
+                    const uint32_t o = ((kk >> 2) * SM::BOX + (kk & 3) * 32) >> 4;
+                    mma_ss(T_H, dQ + o, dCb + kk * (2048 >> 4), ID_KM, true);
+                }
+                mma_commit(&bars[B_H1DONE]);
             }
         }
     }
@@ -292,6 +486,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         const int t = tid - 128;                       // token row = TMEM lane
         const int t0w = t & ~31;                       // first row of this warp
         const uint32_t lane_off = (uint32_t)t0w << 16;
+        if (NHALF == 2) {  // rows [128,256) of the initial state
+            c_init_half<DQK>(smem, T_C + 128 + lane_off, p.C0 ? p.C0 + ((size_t)bh * DQK + 128 + t) * p.dv + col0 : nullptr,
+                             128 + t, gbase[G_SCAL + 0]);
+            tmem_wait_st();
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(&bars[B_CBREADY]);
+        }
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
             const float *g = gbase + (size_t)k * GW;
@@ -338,43 +540,35 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             tc_fence_before_sync();
             mbar_arrive(&bars[B_PREADY]);
             if (t == 0) TRACE(6);
+            if (NHALF == 2) {  // C pass for rows [128,256) of C (the K~ warps take rows [0,128))
+                const bool last = (k == NCH - 1);
+                if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
+                tc_fence_after_sync();
+                c_pass_half<DQK>(smem, T_C + 128 + lane_off, 128 + t, last, last ? g[G_SCAL + 2] : g[GW + G_SCAL + 0],
+                                 p.C1 + ((size_t)bh * DQK + 128 + t) * p.dv + col0);
+                if (!last) {
+                    tmem_wait_st();
+                    fence_proxy_async_smem();
+                    tc_fence_before_sync();
+                    mbar_arrive(&bars[B_CBREADY]);
+                }
+            }
         }
     } else if (warp >= 8 && warp < 12) {
-        // ================= Q~ = Q * e^{m-x_t} dqk^-1/2 in place, q . n =================
+        // ================= Q~ = Q * e^{m-x_t} dqk^-1/2 in place and q . n: first half of the boxes ==========
         const int t = tid - 256;
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
-            const uint32_t w2 = pack_bf16(gbase[(size_t)k * GW + G_WINQ + t], gbase[(size_t)k * GW + G_WINQ + t]);
+            float w2[2][4];
+            q_pass_scales(gbase + (size_t)k * GW + G_WINQ, warp - 8, lane, w2);
             if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
-            // n of the previous tile complete (tile 0: written by the prologue)
+            // n of the previous tile complete (tile 0: written by the prologue); the previous epilogue has
+            // read and cleared s_qn (it arrives on HFREE afterwards)
             if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
-            if (t == 0) TRACE(9);
-            float qn0 = 0.f, qn1 = 0.f;
-#pragma unroll 1
-            for (int q = 0; q < NBOX; ++q) {
-                unsigned char *rowp = smem + SM::Q + q * SM::BOX + t * 128;
-                uint4 v[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(rowp + (((c + t) & 7) << 4));
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int pc = (c + t) & 7;                    // physical 16-byte chunk (rotation spreads banks)
-                    const int j0 = q * 64 + ((pc ^ (t & 7)) << 3);  // logical column of that chunk
-                    const float4 na = *reinterpret_cast<const float4 *>(s_n + j0);
-                    const float4 nb = *reinterpret_cast<const float4 *>(s_n + j0 + 4);
-                    const float2 f0 = unpack_bf16(v[c].x), f1 = unpack_bf16(v[c].y);
-                    const float2 f2 = unpack_bf16(v[c].z), f3 = unpack_bf16(v[c].w);
-                    qn0 += f0.x * na.x + f0.y * na.y + f1.x * na.z + f1.y * na.w;
-                    qn1 += f2.x * nb.x + f2.y * nb.y + f3.x * nb.z + f3.y * nb.w;
-                    v[c].x = mul_bf16x2(v[c].x, w2); v[c].y = mul_bf16x2(v[c].y, w2);
-                    v[c].z = mul_bf16x2(v[c].z, w2); v[c].w = mul_bf16x2(v[c].w, w2);
-                }
-#pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(rowp + (((c + t) & 7) << 4)) = v[c];
-            }
-            // the epilogue of the previous tile has read its q . n (it arrives on HFREE afterwards)
             if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
-            s_qn[t] = qn0 + qn1;
+            if (t == 0) TRACE(9);
+            q_pass_boxes<DQK, 0, NBOX / 2>(smem, s_n, s_qn, w2, warp - 8, lane);
+            if (t == 0) TRACE(10);
             fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor-core (async) proxy
             mbar_arrive(&bars[B_QSCALED]);
             if (t == 0) TRACE(11);
@@ -384,36 +578,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         const int r = tid - 384;                         // K row / row within a 128-row half of C = TMEM lane
         const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
         const bool has_state = p.C0 != nullptr;
-        // ---- prologue: initial state -> TMEM (pre-scaled by the first decay), Cb and n
+        // ---- prologue: rows [0,128) of the initial state (rows [128,256) by the P warps), and n
         {
-            const float decay0 = gbase[G_SCAL + 0];
-            for (int hf = 0; hf < NHALF; ++hf) {
-                const int j = hf * 128 + r;
-                const float *src = p.C0 + ((size_t)bh * DQK + j) * p.dv + col0;
-#pragma unroll 1
-                for (int c0 = 0; c0 < DVS; c0 += 32) {
-                    uint32_t v[32];
-#pragma unroll
-                    for (int x = 0; x < 32; x += 4) {
-                        float4 f = has_state ? *reinterpret_cast<const float4 *>(src + c0 + x) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        v[x] = __float_as_uint(f.x); v[x + 1] = __float_as_uint(f.y);
-                        v[x + 2] = __float_as_uint(f.z); v[x + 3] = __float_as_uint(f.w);
-                    }
-#pragma unroll
-                    for (int x = 0; x < 32; x += 8) {
-                        uint4 o;
-                        o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
-                        o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
-                        o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
-                        o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
-                        const int c = c0 + x;
-                        *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
-                    }
-#pragma unroll
-                    for (int x = 0; x < 32; ++x) v[x] = __float_as_uint(__uint_as_float(v[x]) * decay0);
-                    tmem_st32(T_C + hf * 128 + lane_off + c0, v);
-                }
-            }
+            c_init_half<DQK>(smem, T_C + lane_off, has_state ? p.C0 + ((size_t)bh * DQK + r) * p.dv + col0 : nullptr, r,
+                             gbase[G_SCAL + 0]);
             for (int j = r; j < DQK; j += 128) s_n[j] = has_state ? p.n0[(size_t)bh * DQK + j] : 0.f;
             tmem_wait_st();
             fence_proxy_async_smem();
@@ -423,9 +591,9 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
             const float *g = gbase + (size_t)k * GW;
-            const uint32_t w2 = pack_bf16(g[G_W + r], g[G_W + r]);
+            const float w = g[G_W + r];
             const bool last = (k == NCH - 1);
-            const float decay_next = last ? 1.0f : g[GW + G_SCAL + 0];
+            const float decay_next = last ? g[G_SCAL + 2] : g[GW + G_SCAL + 0];
             if (!(mbar_wait(&bars[B_KFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
             if (r == 0) TRACE(12);
 #pragma unroll 1
@@ -436,8 +604,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(rowp + (((c + r) & 7) << 4));
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    v[c].x = mul_bf16x2(v[c].x, w2); v[c].y = mul_bf16x2(v[c].y, w2);
-                    v[c].z = mul_bf16x2(v[c].z, w2); v[c].w = mul_bf16x2(v[c].w, w2);
+                    const float2 f0 = unpack_bf16(v[c].x), f1 = unpack_bf16(v[c].y);
+                    const float2 f2 = unpack_bf16(v[c].z), f3 = unpack_bf16(v[c].w);
+                    v[c].x = pack_bf16(f0.x * w, f0.y * w); v[c].y = pack_bf16(f1.x * w, f1.y * w);
+                    v[c].z = pack_bf16(f2.x * w, f2.y * w); v[c].w = pack_bf16(f3.x * w, f3.y * w);
                 }
 #pragma unroll
                 for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(rowp + (((c + r) & 7) << 4)) = v[c];
@@ -450,50 +620,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
             tc_fence_after_sync();
             if (r == 0) TRACE(14);
-            for (int hf = 0; hf < NHALF; ++hf) {
-                const int j = hf * 128 + r;
-#pragma unroll 1
-                for (int c0 = 0; c0 < DVS; c0 += 64) {
-                    uint32_t va[32], vb[32];
-                    tmem_ld32(T_C + hf * 128 + lane_off + c0, va);
-                    tmem_ld32(T_C + hf * 128 + lane_off + c0 + 32, vb);
-                    tmem_wait_ld();
-                    if (last) {
-                        float *dst = p.C1 + ((size_t)bh * DQK + j) * p.dv + col0 + c0;
-#pragma unroll
-                        for (int x = 0; x < 32; x += 4) {
-                            *reinterpret_cast<float4 *>(dst + x) = make_float4(__uint_as_float(va[x]), __uint_as_float(va[x + 1]),
-                                                                                __uint_as_float(va[x + 2]), __uint_as_float(va[x + 3]));
-                            *reinterpret_cast<float4 *>(dst + 32 + x) = make_float4(__uint_as_float(vb[x]), __uint_as_float(vb[x + 1]),
-                                                                                     __uint_as_float(vb[x + 2]), __uint_as_float(vb[x + 3]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < 32; x += 8) {
-                            uint4 o;
-                            o.x = pack_bf16(__uint_as_float(va[x]), __uint_as_float(va[x + 1]));
-                            o.y = pack_bf16(__uint_as_float(va[x + 2]), __uint_as_float(va[x + 3]));
-                            o.z = pack_bf16(__uint_as_float(va[x + 4]), __uint_as_float(va[x + 5]));
-                            o.w = pack_bf16(__uint_as_float(va[x + 6]), __uint_as_float(va[x + 7]));
-                            int c = c0 + x;
-                            *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
-                            o.x = pack_bf16(__uint_as_float(vb[x]), __uint_as_float(vb[x + 1]));
-                            o.y = pack_bf16(__uint_as_float(vb[x + 2]), __uint_as_float(vb[x + 3]));
-                            o.z = pack_bf16(__uint_as_float(vb[x + 4]), __uint_as_float(vb[x + 5]));
-                            o.w = pack_bf16(__uint_as_float(vb[x + 6]), __uint_as_float(vb[x + 7]));
-                            c += 32;
-                            *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
-                        }
-#pragma unroll
-                        for (int x = 0; x < 32; ++x) {
-                            va[x] = __float_as_uint(__uint_as_float(va[x]) * decay_next);
-                            vb[x] = __float_as_uint(__uint_as_float(vb[x]) * decay_next);
-                        }
-                        tmem_st32(T_C + hf * 128 + lane_off + c0, va);
-                        tmem_st32(T_C + hf * 128 + lane_off + c0 + 32, vb);
-                    }
-                }
-            }
+            c_pass_half<DQK>(smem, T_C + lane_off, r, last, decay_next, p.C1 + ((size_t)bh * DQK + r) * p.dv + col0);
             if (r == 0) TRACE(15);
             if (!last) {
                 tmem_wait_st();
@@ -503,46 +630,68 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             }
         }
     } else if (warp >= 16) {
-        // ================= normaliser update n' = decay n + colsum(K~); H epilogue =================
+        // ===== second half of the Q~ boxes; normaliser update n' = decay n + colsum(K~); H epilogue =====
         const int r = tid - 512;                         // token row of H = TMEM lane
         const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
         __nv_bfloat16 *hrow = p.h + b * p.sh_b + hd * p.sh_h + col0;
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
-            const float decay = gbase[(size_t)k * GW + G_SCAL + 0];
+            const float *g = gbase + (size_t)k * GW;
+            const float decay = g[G_SCAL + 0];
             const bool last = (k == NCH - 1);
-            // K~ complete, and q . n of this tile has finished reading n
-            if (!(mbar_wait(&bars[B_KSCALED], ph, abort_flag) && mbar_wait(&bars[B_QSCALED], ph, abort_flag))) break;
-            {
-                const int q = r >> 5, cp = r & 31;   // warp -> 64-column box, lane -> column pair
-                if (q < NBOX) {
-                    const unsigned char *box = smem + SM::K + q * SM::BOX + ((cp & 3) << 2);
-                    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+            float w2[2][4];
+            q_pass_scales(g + G_WINQ, warp - 16, lane, w2);
+            if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
+            if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
+            if (r == 0) TRACE(19);
+            q_pass_boxes<DQK, NBOX / 2, NBOX>(smem, s_n, s_qn, w2, warp - 16, lane);
+            if (r == 0) TRACE(20);
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[B_QSCALED]);
+            // column sums of K~
+            if (!mbar_wait(&bars[B_KSCALED], ph, abort_flag)) break;
+            if (r == 0) TRACE(22);
+            const int q = r >> 5, cp = r & 31;   // warp -> 64-column box, lane -> column pair
+            float s0 = 0.f, s1 = 0.f;
+            if (q < NBOX) {
+                const unsigned char *box = smem + SM::K + q * SM::BOX + ((cp & 3) << 2);
+                float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 8
-                    for (int tt = 0; tt < LT; tt += 4) {
+                for (int tt = 0; tt < LT; tt += 4) {
 #pragma unroll
-                        for (int x = 0; x < 4; ++x) {
-                            const uint32_t off = (tt + x) * 128 + ((((cp >> 2) ^ ((tt + x) & 7))) << 4);
-                            const float2 f = unpack_bf16(*reinterpret_cast<const uint32_t *>(box + off));
-                            a0[x] += f.x; a1[x] += f.y;
-                        }
+                    for (int x = 0; x < 4; ++x) {
+                        const uint32_t off = (tt + x) * 128 + ((((cp >> 2) ^ ((tt + x) & 7))) << 4);
+                        const float2 f = unpack_bf16(*reinterpret_cast<const uint32_t *>(box + off));
+                        a0[x] += f.x; a1[x] += f.y;
                     }
-                    const int j = q * 64 + cp * 2;
-                    const float n0v = decay * s_n[j] + ((a0[0] + a0[1]) + (a0[2] + a0[3]));
-                    const float n1v = decay * s_n[j + 1] + ((a1[0] + a1[1]) + (a1[2] + a1[3]));
-                    s_n[j] = n0v;
-                    s_n[j + 1] = n1v;
-                    if (last && blockIdx.y == 0) { p.n1[(size_t)bh * DQK + j] = n0v; p.n1[(size_t)bh * DQK + j + 1] = n1v; }
+                }
+                s0 = (a0[0] + a0[1]) + (a0[2] + a0[3]);
+                s1 = (a1[0] + a1[1]) + (a1[2] + a1[3]);
+            }
+            if (r == 0) TRACE(21);
+            mbar_arrive(&bars[B_KREAD]);   // K~ no longer read by the CUDA cores: the tile may be reloaded
+            // n is rewritten only after every q . n of this tile has been taken
+            if (!mbar_wait(&bars[B_QSCALED], ph, abort_flag)) break;
+            if (q < NBOX) {
+                const int j = q * 64 + cp * 2;
+                const float n0v = decay * s_n[j] + s0, n1v = decay * s_n[j + 1] + s1;
+                s_n[j] = n0v;
+                s_n[j + 1] = n1v;
+                if (last && blockIdx.y == 0) {
+                    const float fr = g[G_SCAL + 2];   // n = n~ e^{rho}
+                    p.n1[(size_t)bh * DQK + j] = n0v * fr; p.n1[(size_t)bh * DQK + j + 1] = n1v * fr;
                 }
             }
-            mbar_arrive(&bars[B_NDONE]);  // K~ no longer read by the CUDA cores; n of this tile final
+            mbar_arrive(&bars[B_NDONE]);
             // epilogue: h = H / (max(|den|, e^{-m_t}) + eps)
-            if (!(mbar_wait(&bars[B_PREADY], ph, abort_flag) && mbar_wait(&bars[B_H2DONE], ph, abort_flag))) break;
+            if (!(mbar_wait(&bars[B_PREADY], ph, abort_flag) && mbar_wait(&bars[B_H2DONE], ph, abort_flag) &&
+                  mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
             tc_fence_after_sync();
             if (r == 0) TRACE(7);
-            const float winq = __bfloat162float(__float2bfloat16_rn(gbase[(size_t)k * GW + G_WINQ + r]));  // the scale Q~ really carries
+            const float winq = g[G_WINQ + r];
             const float den = s_qn[r] * winq + s_rs[ph * LT + r];
-            const float inv = 1.0f / (fmaxf(fabsf(den), gbase[(size_t)k * GW + G_EMT + r]) + p.eps);
+            s_qn[r] = 0.f;
+            const float inv = 1.0f / (fmaxf(fabsf(den), g[G_EMT + r]) + p.eps);
             __nv_bfloat16 *hp = hrow + (int64_t)(k * LT + r) * p.sh_s;
 #pragma unroll 1
             for (int c0 = 0; c0 < DVS; c0 += 64) {
@@ -588,7 +737,7 @@ bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype) {
     if (dtype != XLSTM_BF16) return false;
     if (p.dqk != 256 && p.dqk != 128) return false;
     if (p.dv % DVS) return false;
-    if (p.S < LT) return false;
+    if (p.S < LT || p.S / LT > 6000) return false;  // gate pre-pass keeps 32 bytes per tile in shared memory
     for (int d = 0; d < 3; ++d)
         if (p.sq[d] % 8 || p.sk[d] % 8 || p.sv[d] % 8 || p.sh[d] % 8) return false;  // 16-byte TMA / store alignment
     if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
@@ -619,9 +768,16 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
     const bool tail = s_full < p.S;
     if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return XLSTM_ERR_CUDA;
 
-    mlstm_gate_prep_kernel<__nv_bfloat16><<<BH, 32, 0, st>>>(
-        static_cast<const __nv_bfloat16 *>(p.ig), static_cast<const __nv_bfloat16 *>(p.fg), p.sg[0], p.sg[1], p.sg[2],
-        p.C0 ? p.m0 : nullptr, gates, tail ? tail_m : p.m1, p.NH, nch, p.qscale);
+    {
+        auto gk = mlstm_gate_prep_kernel<__nv_bfloat16>;
+        const size_t gsm = 4 * (size_t)nch * sizeof(double);
+        if (gsm > 48 * 1024 &&
+            cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm) != cudaSuccess)
+            return XLSTM_ERR_CUDA;
+        gk<<<BH, GP_THREADS, gsm, st>>>(static_cast<const __nv_bfloat16 *>(p.ig), static_cast<const __nv_bfloat16 *>(p.fg),
+                                        p.sg[0], p.sg[1], p.sg[2], p.C0 ? p.m0 : nullptr, gates, tail ? tail_m : p.m1,
+                                        p.NH, nch, p.qscale);
+    }
     if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
 
     TcParams tp{};
