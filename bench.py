@@ -369,7 +369,7 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of mlstm_step_kernel, from the ncu
 # capture summarised under profiles/ (None until a capture exists)
-TRAFFIC_PER_LAUNCH = None
+TRAFFIC_PER_LAUNCH = 84_321_792   # 67.52 MB read + 16.80 MB written before the kernel ends (rest drains from L2 later)
 
 
 def run_prefill(torch, dist, ops, device, world, rank, args):

@@ -241,6 +241,58 @@ def test_extreme_gates_stay_finite(ops):
     assert np.abs(host(st[2]) - st_ref[2]).max() < 1e-3
 
 
+def test_chunkwise_bf16_extreme_gates_tensor_core_path(ops):
+    """bf16 tensor-core path with gates pinned at the soft-cap limits for long stretches: every exponent is a
+    non-positive difference and the TMEM state is rescaled lazily, so nothing may overflow.  The final state
+    must meet the bf16 tolerance against the float64 recurrence.  With such gates the normaliser q.n + sum(P)
+    of many tokens is a near-cancellation (|h| reaches 1e4): there h = num/den amplifies the bf16 rounding of
+    the weights by 1/|den| in ANY bf16 implementation, so h is compared on the well-conditioned tokens
+    (|h| <= 5 in the float64 result, the usual range of h; 62 % of the tokens here) and only checked for finiteness elsewhere."""
+    rng = np.random.default_rng(13)
+    B, NH, S, dqk, dv = 1, 2, 768, 256, 256
+    q, k = (xo.bf16_round(rng.standard_normal((B, NH, S, dqk)).astype(np.float32)) for _ in range(2))
+    v = xo.bf16_round(rng.standard_normal((B, NH, S, dv)).astype(np.float32))
+    i = np.repeat(rng.choice([-15.0, 0.0, 15.0], size=(B, NH, S // 16)), 16, axis=-1).astype(np.float32)
+    f = np.repeat(rng.choice([-15.0, 3.0, 15.0], size=(B, NH, S // 32), p=[0.1, 0.5, 0.4]), 32, axis=-1).astype(np.float32)
+    h64, st64 = recurrent_fp64(q, k, v, i, f)
+    bf = torch.bfloat16
+    assert ops.chunkwise_workspace_bytes(B, NH, S, dqk, dv, 64, bf) > 0  # really the tensor-core path
+    h, st = ops.mlstm_chunkwise(*(dev(a, bf) for a in (q, k, v, i, f)))
+    assert np.isfinite(host(h)).all() and np.isfinite(host(st[0])).all()
+    ok = np.abs(h64).max(axis=-1, keepdims=True) <= 5.0
+    assert ok.mean() > 0.5
+    assert relerr(np.where(ok, host(h), 0.0), np.where(ok, h64, 0.0)) < BF16_TOL
+    assert relerr(host(st[0]), st64[0]) < BF16_TOL and relerr(host(st[1]), st64[1]) < BF16_TOL
+    assert np.abs(host(st[2]) - st64[2]).max() < 1e-3
+
+
+def test_chunkwise_full_length_properties(ops):
+    """BASELINE configs[3] length (S = 32768, 256/512, bf16): the oracle cannot run this in seconds, so check
+    (a) the first 384 tokens against the oracle, (b) one pass == two half passes with the carried state,
+    (c) run-to-run bitwise determinism."""
+    B, NH, S, dqk, dv = 1, 4, 32768, 256, 512
+    g = torch.Generator().manual_seed(3)
+    bf = torch.bfloat16
+    q = torch.randn(B, NH, S, dqk, generator=g).to(bf)
+    k = torch.randn(B, NH, S, dqk, generator=g).to(bf)
+    v = torch.randn(B, NH, S, dv, generator=g).to(bf)
+    i = (15 * torch.tanh(torch.randn(B, NH, S, generator=g) / 15)).to(bf)
+    f = (15 * torch.tanh((torch.randn(B, NH, S, generator=g) + 3) / 15)).to(bf)
+    P = 384
+    h_ref, _ = xo.mlstm_recurrent(*(t[:, :, :P].float().numpy() for t in (q, k, v, i, f)))
+    qd, kd, vd, idv, fd = (t.cuda() for t in (q, k, v, i, f))
+    h, st = ops.mlstm_chunkwise(qd, kd, vd, idv, fd)
+    assert relerr(host(h[:, :, :P]), h_ref) < BF16_TOL
+    H = S // 2
+    h1, st1 = ops.mlstm_chunkwise(qd[:, :, :H], kd[:, :, :H], vd[:, :, :H], idv[:, :, :H], fd[:, :, :H])
+    h2, st2 = ops.mlstm_chunkwise(qd[:, :, H:], kd[:, :, H:], vd[:, :, H:], idv[:, :, H:], fd[:, :, H:], st1)
+    assert relerr(host(torch.cat([h1, h2], 2)), host(h)) < BF16_TOL
+    assert relerr(host(st2[0]), host(st[0])) < BF16_TOL and np.abs(host(st2[2]) - host(st[2])).max() < 1e-3
+    assert torch.isfinite(h.float()).all()
+    h_again, _ = ops.mlstm_chunkwise(qd, kd, vd, idv, fd)
+    assert torch.equal(h, h_again)
+
+
 # ---- sLSTM ------------------------------------------------------------------------
 @pytest.mark.parametrize("tag", ["a", "b", "x", "z"])
 def test_slstm_scan_fixture(ops, golden, tag):

@@ -524,10 +524,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                             if (j > lane) p0 = 0.f;
                             if (j + 1 > lane) p1 = 0.f;
                         }
-                        const uint32_t pk = pack_bf16(p0, p1);
-                        const float2 pr = unpack_bf16(pk);
-                        rowsum += pr.x + pr.y;
-                        packed[j >> 1] = pk;
+                        rowsum += p0 + p1;   // fp32, before rounding: keeps the normaliser well conditioned
+                        packed[j >> 1] = pack_bf16(p0, p1);
                     }
                 } else {
 #pragma unroll
