@@ -387,15 +387,20 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
     w_out = (torch.randn(NH * DV, NH * DV, generator=g) * 0.02).to(bf).to(device)
     need = ops.chunkwise_workspace_bytes(Bp, nh_local, Sp, DQK, DV, L, bf)
     ws = torch.empty(max(need, 1), dtype=torch.uint8, device=device)
-    gathered = torch.empty(world, Bp, nh_local, Sp, DV, dtype=bf, device=device) if world > 1 else None
+    from xlstm_cuda.parallel import FusedHeadGather, all_gather_heads
+    fused = FusedHeadGather(Bp, Sp, nh_local * world, DV, bf, device) if (world > 1 and NH % world == 0) else None
 
     def one():
+        if fused is not None:   # h tiles stored straight into every rank's [B,S,NH,dv] buffer by the kernel
+            y, _ = fused.run(q, k, v, i, f, None, out_proj=w_out.t(), workspace=ws)
+            return y
         h, st = ops.mlstm_chunkwise(q, k, v, i, f, None, L, 1e-6, ws)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, h)
-            hh = gathered.permute(1, 3, 0, 2, 4).reshape(Bp * Sp, NH * DV)
-        else:
-            hh = h.permute(0, 2, 1, 3).reshape(Bp * Sp, NH * DV)
+        hh = h.permute(0, 2, 1, 3).reshape(Bp * Sp, NH * DV)
+        return hh @ w_out.t()
+
+    def one_nccl():             # the same with a separate NCCL all-gather, for comparison
+        h, st = ops.mlstm_chunkwise(q, k, v, i, f, None, L, 1e-6, ws)
+        hh = all_gather_heads(h).permute(0, 2, 1, 3).reshape(Bp * Sp, NH * DV)
         return hh @ w_out.t()
 
     e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
@@ -416,18 +421,26 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
         one()
     e[3].record()
     torch.cuda.synchronize()
-    t_cell = torch.tensor([e[0].elapsed_time(e[1]) / reps, e[2].elapsed_time(e[3]) / reps], device=device)
+    nccl_ms = 0.0
+    if world > 1:
+        one_nccl()
+        torch.cuda.synchronize()
+        dist.barrier()
+        nccl_ms = _time_cuda(torch, one_nccl, reps)
+    t_cell = torch.tensor([e[0].elapsed_time(e[1]) / reps, e[2].elapsed_time(e[3]) / reps, nccl_ms], device=device)
     if world > 1:
         dist.all_reduce(t_cell, op=dist.ReduceOp.MAX)
-    cell_ms, full_ms = (float(x) for x in t_cell)
+    cell_ms, full_ms, nccl_ms = (float(x) for x in t_cell)
     tokens = Bp * Sp
     flop = tokens * NH * (4 * DQK * DV + L * (DQK + DV))      # whole job, causal-half count
     byts = tokens * NH * ((2 * DQK + 2 * DV) * 2 + 2 * 2)
     hbm, tf, which = peaks()
     return {"workload": f"mlstm_chunkwise_prefill B={Bp} S={Sp} NH={NH} dqk={DQK} dv={DV} L={L} bf16 (BASELINE configs[3])",
-            "parallelism": f"heads sharded x{world}, all-gather h, replicated out-proj", "scaling": "strong",
+            "parallelism": f"heads sharded x{world}, fused all-gather of h, replicated out-proj", "scaling": "strong",
             "cell_tokens_per_s": tokens / (cell_ms * 1e-3), "cell_ms": cell_ms,
             "with_allgather_outproj_tokens_per_s": tokens / (full_ms * 1e-3), "with_allgather_outproj_ms": full_ms,
+            "gather": ("fused: kernel epilogue stores h into every rank's buffer over NVLink" if world > 1 else "single rank"),
+            "nccl_allgather_variant_ms": (nccl_ms if world > 1 else None),
             "roofline": {"bound": "tensor", "achieved": flop / world / (cell_ms * 1e-3) / 1e12, "peak": tf,
                          "unit": "TFLOP/s", "frac": flop / world / (cell_ms * 1e-3) / 1e12 / tf,
                          "hbm_achieved_gbs": byts / world / (cell_ms * 1e-3) / 1e9, "hbm_frac": byts / world / (cell_ms * 1e-3) / 1e9 / hbm,

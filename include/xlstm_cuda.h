@@ -98,6 +98,25 @@ int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const void *v, const
 size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int dv, int L, int dtype);
 
 /*
+ * xlstm_mlstm_chunkwise_fwd fused with the all-gather of h for head-sharded execution: the
+ * epilogue stores every h tile to `h` AND, with the same strides and offsets, to `n_peers` (<= 7)
+ * further base pointers - the same head slot of the peer GPUs' [B,S,NH_total,dv] buffers, mapped
+ * into this process (symmetric memory / IPC).  The stores are plain 16-byte st.global over NVLink
+ * and overlap the tensor-core work tile by tile; after the kernels of all ranks have finished (one
+ * cross-rank barrier) every rank holds the complete h and can run the out-projection on it.
+ * `h_peers` is a HOST array of device pointers.  bf16, tensor-core shapes, S a multiple of 128.
+ * The reference has no multi-device path (its docs say "Single-device only", docs/COMPONENTS.md:4334-4339); this stands in for the
+ * all-gather that precedes mLSTMOutputCell.out_proj
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/mlstm_output_cell.py:84-99) when heads are sharded.
+ */
+int xlstm_mlstm_chunkwise_fwd_gather(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                     const float *C0, const float *n0, const float *m0,
+                                     void *h, float *C1, float *n1, float *m1,
+                                     int B, int NH, int S, int dqk, int dv, int L, float eps, int dtype,
+                                     const int64_t *strides, void *workspace, size_t workspace_bytes,
+                                     void *const *h_peers, int n_peers, void *stream);
+
+/*
  * xlstm_mlstm_chunkwise_fwd for callers that cannot supply scratch memory (no counterpart in
  * the reference: its launchers allocate their outputs through the framework).  Same arguments
  * and results as xlstm_mlstm_chunkwise_fwd without `workspace`; the scratch is an 8 MiB block

@@ -13,6 +13,9 @@ struct ChunkwiseParams {
     float eps, qscale;
     // element strides (batch, head, token); innermost dimension contiguous
     int64_t sq[3], sk[3], sv[3], sh[3], sg[3];
+    // optional extra destinations of h (same strides and offsets as `h`): buffers of peer GPUs
+    void *h_peer[7];
+    int n_peer;
 };
 
 // exact-fp32 CUDA-core path: any dqk <= 512, dv, S, L <= 64

@@ -21,11 +21,11 @@ extern "C" size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, in
     return xl::mlstm_chunkwise_tc_workspace(B, NH, S, dqk, dv, L);
 }
 
-extern "C" int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const void *v, const void *ig, const void *fg,
-                                         const float *C0, const float *n0, const float *m0, void *h, float *C1,
-                                         float *n1, float *m1, int B, int NH, int S, int dqk, int dv, int L,
-                                         float eps, int dtype, const int64_t *strides, void *workspace,
-                                         size_t workspace_bytes, void *stream) {
+static int chunkwise_dispatch(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                              const float *C0, const float *n0, const float *m0, void *h, float *C1,
+                              float *n1, float *m1, int B, int NH, int S, int dqk, int dv, int L,
+                              float eps, int dtype, const int64_t *strides, void *workspace,
+                              size_t workspace_bytes, void *stream, void *const *h_peers, int n_peers) {
     if (!q || !k || !v || !ig || !fg || !h || !C1 || !n1 || !m1) return XLSTM_ERR_INVALID;
     if (B <= 0 || NH <= 0 || S <= 0 || dqk <= 0 || dv <= 0 || L <= 0) return XLSTM_ERR_INVALID;
     if (C0 && (!n0 || !m0)) return XLSTM_ERR_INVALID;
@@ -49,7 +49,16 @@ extern "C" int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const voi
         dense_strides(p);
     }
 
-    if (!xl::mlstm_chunkwise_tc_supported(p, dtype)) return xl::mlstm_chunkwise_simt(p, dtype, st);
+    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !h_peers)) return XLSTM_ERR_INVALID;
+    p.n_peer = n_peers;
+    for (int i = 0; i < n_peers; ++i) {
+        if (!h_peers[i] || (reinterpret_cast<uintptr_t>(h_peers[i]) & 15u)) return XLSTM_ERR_INVALID;
+        p.h_peer[i] = h_peers[i];
+    }
+    if (!xl::mlstm_chunkwise_tc_supported(p, dtype)) {
+        if (n_peers) return XLSTM_ERR_UNSUPPORTED;   // peer stores exist in the tensor-core kernel only
+        return xl::mlstm_chunkwise_simt(p, dtype, st);
+    }
 
     // Whole 128-token tiles on the tensor cores, then the remaining tokens (with the carried
     // state) on the exact path: the split the reference neuron makes between its chunkwise and
@@ -59,4 +68,23 @@ extern "C" int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const voi
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return XLSTM_ERR_WORKSPACE;
     return xl::mlstm_chunkwise_tc(p, workspace, workspace_bytes, st);
+}
+
+extern "C" int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                         const float *C0, const float *n0, const float *m0, void *h, float *C1,
+                                         float *n1, float *m1, int B, int NH, int S, int dqk, int dv, int L,
+                                         float eps, int dtype, const int64_t *strides, void *workspace,
+                                         size_t workspace_bytes, void *stream) {
+    return chunkwise_dispatch(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, S, dqk, dv, L, eps, dtype, strides,
+                              workspace, workspace_bytes, stream, nullptr, 0);
+}
+
+extern "C" int xlstm_mlstm_chunkwise_fwd_gather(const void *q, const void *k, const void *v, const void *ig,
+                                                const void *fg, const float *C0, const float *n0, const float *m0,
+                                                void *h, float *C1, float *n1, float *m1, int B, int NH, int S,
+                                                int dqk, int dv, int L, float eps, int dtype, const int64_t *strides,
+                                                void *workspace, size_t workspace_bytes, void *const *h_peers,
+                                                int n_peers, void *stream) {
+    return chunkwise_dispatch(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, S, dqk, dv, L, eps, dtype, strides,
+                              workspace, workspace_bytes, stream, h_peers, n_peers);
 }

@@ -18,7 +18,7 @@
 // small pre-pass kernel (one warp per head, sequential over tiles) that writes
 // them to caller-provided scratch.
 //
-// Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc),
+// Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc), warp 2 TMA stores of h,
 // warps 4-7 gate matrix P, then the C pass for rows [128,256) of C;
 // warps 8-11 Q~ scaling and q.n for the first half of the dqk boxes;
 // warps 12-15 K~ scaling, then the C pass for rows [0,128) (refresh Cb);
@@ -59,8 +59,8 @@ struct TcParams {
     CUtensorMap tq, tk, tv;
     const float *gates;            // [B*NH][NCH][GW]
     const float *C0, *n0;
-    __nv_bfloat16 *h;
-    int64_t sh_b, sh_h, sh_s;
+    CUtensorMap th[8];             // h of this GPU, then the same head slot of up to 7 peer GPUs' buffers
+    int n_h;                       // number of destinations (1 + peers)
     float *C1, *n1;
     int NH, dv, NCH;
     float eps, log2_qscale;
@@ -204,7 +204,7 @@ template <int DQK> struct Smem {
 };
 
 enum { B_QFULL = 0, B_KFULL, B_VFULL, B_SDONE, B_H1DONE, B_UPDDONE, B_H2DONE, B_QSCALED, B_KSCALED, B_CBREADY,
-       B_PREADY, B_HFREE, B_NDONE, B_KREAD, B_NBARS };
+       B_PREADY, B_HFREE, B_NDONE, B_KREAD, B_HSTAGED, B_VFREE, B_NBARS };
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -389,6 +389,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         mbar_init(&bars[B_H2DONE], 1);
         mbar_init(&bars[B_QSCALED], 256); mbar_init(&bars[B_KSCALED], 128); mbar_init(&bars[B_CBREADY], 128 * NHALF);
         mbar_init(&bars[B_PREADY], 128);  mbar_init(&bars[B_HFREE], 128);   mbar_init(&bars[B_NDONE], 128);  mbar_init(&bars[B_KREAD], 128);
+        mbar_init(&bars[B_HSTAGED], 128); mbar_init(&bars[B_VFREE], 1);
         mbar_fence_init();
         tma_prefetch_desc(&p.tq); tma_prefetch_desc(&p.tk); tma_prefetch_desc(&p.tv);
     }
@@ -404,7 +405,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         // ================= TMA producer =================
         // Q is free once the read-out MMA of the previous tile has run (and the scaling warps are
         // done with it: they finish before that MMA is issued); K once the state update has run
-        // and the normaliser sums are taken; V once both its consumers (update, P V) have run.
+        // and the normaliser sums are taken; V once both its consumers (update, P V) have run AND the
+        // h tile that the epilogue stages in the V buffer has been read by its TMA stores.
         if (lane == 0) {
             for (int k = 0; k < NCH; ++k) {
                 const int t0 = k * LT;
@@ -413,14 +415,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 TRACE(17);
                 mbar_expect_tx(&bars[B_KFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::K + q * SM::BOX, &p.tk, &bars[B_KFULL], q * 64, t0, hd, b);
-                if (k > 0 && !mbar_wait(&bars[B_H2DONE], (k - 1) & 1, abort_flag)) break;
-                TRACE(18);
-                mbar_expect_tx(&bars[B_VFULL], 2 * SM::BOX);
-                for (int q = 0; q < 2; ++q) tma_load_4d(smem + SM::V + q * SM::BOX, &p.tv, &bars[B_VFULL], col0 + q * 64, t0, hd, b);
                 if (k > 0 && !mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag)) break;
                 TRACE(16);
                 mbar_expect_tx(&bars[B_QFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[B_QFULL], q * 64, t0, hd, b);
+                if (k > 0 && !mbar_wait(&bars[B_VFREE], (k - 1) & 1, abort_flag)) break;   // h tile staged in V has been stored
+                TRACE(18);
+                mbar_expect_tx(&bars[B_VFULL], 2 * SM::BOX);
+                for (int q = 0; q < 2; ++q) tma_load_4d(smem + SM::V + q * SM::BOX, &p.tv, &bars[B_VFULL], col0 + q * 64, t0, hd, b);
             }
         }
     } else if (warp == 1) {
@@ -479,6 +481,21 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 }
                 mma_commit(&bars[B_H1DONE]);
             }
+        }
+    }
+    else if (warp == 2) {
+        // ================= h store: TMA from the staged tile to this GPU's h and to the peers =================
+        if (lane == 0) {
+            for (int k = 0; k < NCH; ++k) {
+                if (!mbar_wait(&bars[B_HSTAGED], k & 1, abort_flag)) break;
+                for (int d = 0; d < p.n_h; ++d)
+                    for (int bx = 0; bx < 2; ++bx)
+                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, k * LT, hd, b);
+                tma_store_commit();
+                tma_store_wait_read();            // staging tile consumed: V may be reloaded
+                mbar_arrive(&bars[B_VFREE]);
+            }
+            tma_store_wait_all();                 // all h writes performed before the CTA exits
         }
     }
     else if (warp >= 4 && warp < 8) {
@@ -631,7 +648,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         // ===== second half of the Q~ boxes; normaliser update n' = decay n + colsum(K~); H epilogue =====
         const int r = tid - 512;                         // token row of H = TMEM lane
         const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
-        __nv_bfloat16 *hrow = p.h + b * p.sh_b + hd * p.sh_h + col0;
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
             const float *g = gbase + (size_t)k * GW;
@@ -690,13 +706,16 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             const float den = s_qn[r] * winq + s_rs[ph * LT + r];
             s_qn[r] = 0.f;
             const float inv = 1.0f / (fmaxf(fabsf(den), g[G_EMT + r]) + p.eps);
-            __nv_bfloat16 *hp = hrow + (int64_t)(k * LT + r) * p.sh_s;
+            // H -> bf16 h tile staged in the (now idle) V buffer, in the swizzled box layout of the h
+            // tensor maps; one thread then issues TMA stores to this GPU's h and to every peer's buffer
+            unsigned char *stage = smem + SM::V + r * 128;
 #pragma unroll 1
             for (int c0 = 0; c0 < DVS; c0 += 64) {
                 uint32_t va[32], vb[32];
                 tmem_ld32(T_H + lane_off + c0, va);
                 tmem_ld32(T_H + lane_off + c0 + 32, vb);
                 tmem_wait_ld();
+                unsigned char *box = stage + (c0 >> 6) * SM::BOX;
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 o;
@@ -704,20 +723,18 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                     o.y = pack_bf16(__uint_as_float(va[j + 2]) * inv, __uint_as_float(va[j + 3]) * inv);
                     o.z = pack_bf16(__uint_as_float(va[j + 4]) * inv, __uint_as_float(va[j + 5]) * inv);
                     o.w = pack_bf16(__uint_as_float(va[j + 6]) * inv, __uint_as_float(va[j + 7]) * inv);
-                    *reinterpret_cast<uint4 *>(hp + c0 + j) = o;
-                }
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    uint4 o;
+                    *reinterpret_cast<uint4 *>(box + ((((j >> 3)) ^ (r & 7)) << 4)) = o;
                     o.x = pack_bf16(__uint_as_float(vb[j]) * inv, __uint_as_float(vb[j + 1]) * inv);
                     o.y = pack_bf16(__uint_as_float(vb[j + 2]) * inv, __uint_as_float(vb[j + 3]) * inv);
                     o.z = pack_bf16(__uint_as_float(vb[j + 4]) * inv, __uint_as_float(vb[j + 5]) * inv);
                     o.w = pack_bf16(__uint_as_float(vb[j + 6]) * inv, __uint_as_float(vb[j + 7]) * inv);
-                    *reinterpret_cast<uint4 *>(hp + c0 + 32 + j) = o;
+                    *reinterpret_cast<uint4 *>(box + ((((j >> 3) + 4) ^ (r & 7)) << 4)) = o;
                 }
             }
             tc_fence_before_sync();
-            mbar_arrive(&bars[B_HFREE]);
+            mbar_arrive(&bars[B_HFREE]);          // H in TMEM has been read
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[B_HSTAGED]);
             if (r == 0) TRACE(8);
         }
     }
@@ -764,6 +781,7 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
     float *tail_n = gates + (size_t)BH * nch * GW;
     float *tail_m = tail_n + (size_t)BH * p.dqk;
     const bool tail = s_full < p.S;
+    if (tail && p.n_peer) return XLSTM_ERR_UNSUPPORTED;   // the exact tail path writes the local h only
     if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return XLSTM_ERR_CUDA;
 
     {
@@ -785,8 +803,10 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
         return XLSTM_ERR_UNSUPPORTED;
     tp.gates = gates;
     tp.C0 = p.C0; tp.n0 = p.n0;
-    tp.h = static_cast<__nv_bfloat16 *>(p.h);
-    tp.sh_b = p.sh[0]; tp.sh_h = p.sh[1]; tp.sh_s = p.sh[2];
+    tp.n_h = 1 + p.n_peer;
+    for (int i = 0; i < tp.n_h; ++i)
+        if (!make_tmap_bf16_4d(&tp.th[i], i == 0 ? p.h : p.h_peer[i - 1], p.dv, s_full, p.NH, p.B, p.sh[2], p.sh[1], p.sh[0], LT))
+            return XLSTM_ERR_UNSUPPORTED;
     tp.C1 = p.C1; tp.n1 = tail ? tail_n : p.n1;
     tp.NH = p.NH; tp.dv = p.dv; tp.NCH = nch; tp.eps = p.eps; tp.log2_qscale = log2f(p.qscale); tp.status = status;
     dim3 grid(BH, p.dv / DVS);

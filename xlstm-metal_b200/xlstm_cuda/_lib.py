@@ -20,6 +20,9 @@ _SIGNATURES = {
     "xlstm_mlstm_step": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 4 + [c_float, c_int, c_void_p]),
     "xlstm_mlstm_chunkwise_fwd": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6
                                   + [c_float, c_int, ctypes.POINTER(c_int64), c_void_p, c_size_t, c_void_p]),
+    "xlstm_mlstm_chunkwise_fwd_gather": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6
+                                         + [c_float, c_int, ctypes.POINTER(c_int64), c_void_p, c_size_t,
+                                            ctypes.POINTER(c_void_p), c_int, c_void_p]),
     "xlstm_mlstm_chunkwise_workspace_bytes": (c_size_t, [c_int] * 7),
     "xlstm_mlstm_chunkwise_fwd_static": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6
                                          + [c_float, c_int, ctypes.POINTER(c_int64), c_void_p]),

@@ -91,9 +91,14 @@ def chunkwise_workspace_bytes(B, NH, S, dqk, dv, L, dtype: torch.dtype) -> int:
 
 
 def mlstm_chunkwise(q, k, v, i, f, state=None, chunk_size: int = 64, eps: float = 1e-6,
-                    workspace: Optional[torch.Tensor] = None):
+                    workspace: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None,
+                    h_peer_ptrs=None):
     """Chunkwise forward.  q,k: [B,NH,S,dqk]; v: [B,NH,S,dv]; i,f: [B,NH,S] (any strides with a
-    contiguous last dimension, e.g. the permuted [B,S,NH,d] projection output)."""
+    contiguous last dimension, e.g. the permuted [B,S,NH,d] projection output).
+
+    ``h_out`` (optional) is a ``[B,NH,S,dv]`` view to write h into (e.g. a head slice of a
+    ``[B,S,NH_total,dv]`` buffer); ``h_peer_ptrs`` (optional) are raw device pointers to the same
+    slot in peer GPUs' buffers: the kernel stores every h tile there too (fused all-gather)."""
     _need_cuda(q, k, v, i, f)
     B, NH, S, dqk = q.shape
     dv = v.shape[-1]
@@ -109,7 +114,12 @@ def mlstm_chunkwise(q, k, v, i, f, state=None, chunk_size: int = 64, eps: float 
     else:
         C0 = n0 = m0 = None
     dev = q.device
-    h = torch.empty(B, NH, S, dv, dtype=q.dtype, device=dev)
+    if h_out is not None:
+        if tuple(h_out.shape) != (B, NH, S, dv) or h_out.dtype != q.dtype or h_out.stride(-1) != 1:
+            raise ValueError("h_out must be a [B,NH,S,dv] view of the activation dtype with a contiguous last dimension")
+        h = h_out
+    else:
+        h = torch.empty(B, NH, S, dv, dtype=q.dtype, device=dev)
     C1 = torch.empty(B, NH, dqk, dv, dtype=torch.float32, device=dev)
     n1 = torch.empty(B, NH, dqk, dtype=torch.float32, device=dev)
     m1 = torch.empty(B, NH, dtype=torch.float32, device=dev)
@@ -119,6 +129,13 @@ def mlstm_chunkwise(q, k, v, i, f, state=None, chunk_size: int = 64, eps: float 
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty(need, dtype=torch.uint8, device=dev)
     wbytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    if h_peer_ptrs:
+        peers = (ctypes.c_void_p * len(h_peer_ptrs))(*[int(x) for x in h_peer_ptrs])
+        _lib.check(_lib.load().xlstm_mlstm_chunkwise_fwd_gather(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
+            h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, S, dqk, dv, int(chunk_size), float(eps),
+            dt, sarr, _ptr(workspace), wbytes, peers, len(h_peer_ptrs), _stream()), "xlstm_mlstm_chunkwise_fwd_gather")
+        return h, (C1, n1, m1)
     _lib.check(_lib.load().xlstm_mlstm_chunkwise_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
         h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, S, dqk, dv, int(chunk_size), float(eps), dt,

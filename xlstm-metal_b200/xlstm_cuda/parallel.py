@@ -69,4 +69,49 @@ def head_sharded_prefill(cell: Callable, q, k, v, i, f, state=None, out_proj: Op
     return h.permute(0, 2, 1, 3).reshape(B, S, NH * dv) @ out_proj, st_local
 
 
-__all__ = ["head_range", "batch_range", "shard_heads", "all_gather_heads", "head_sharded_prefill"]
+class FusedHeadGather:
+    """Head-sharded chunkwise prefill whose all-gather is done by the kernel itself.
+
+    Every rank owns a ``[B, S, NH, dv]`` buffer in symmetric memory (the layout the out-projection
+    GEMM reads, so no permute is needed afterwards).  The chunkwise kernel of rank r writes each h
+    tile of its heads into its own buffer AND, with plain stores over NVLink, into the same slot of
+    every peer's buffer while the tensor cores work on the next tile; one cross-rank barrier later
+    every rank holds all heads.  No NCCL call and no extra pass over h.
+    """
+
+    def __init__(self, B: int, S: int, NH: int, dv: int, dtype: torch.dtype, device, group=None):
+        self.B, self.S, self.NH, self.dv = B, S, NH, dv
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
+        self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+        self.lo, self.hi = head_range(NH, self.world, self.rank)
+        self.handle = None
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buf = symm_mem.empty(B, S, NH, dv, dtype=dtype, device=device)
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+            esz = self.buf.element_size()
+            slot = self.lo * dv * esz   # byte offset of this rank's first head inside any rank's buffer
+            self.peer_ptrs = [int(ptr) + slot for r, ptr in enumerate(self.handle.buffer_ptrs) if r != self.rank]
+        else:
+            self.buf = torch.empty(B, S, NH, dv, dtype=dtype, device=device)
+            self.peer_ptrs = []
+        self.h_view = self.buf[:, :, self.lo:self.hi, :].permute(0, 2, 1, 3)   # [B, NH/G, S, dv] strided
+
+    def barrier(self) -> None:
+        if self.handle is not None:
+            self.handle.barrier()
+
+    def run(self, q, k, v, i, f, state=None, out_proj: Optional[torch.Tensor] = None, workspace=None):
+        """q, k, v, i, f hold THIS rank's heads (``[B, NH/G, S, d]``).  Returns ``(y or h_all, state)``
+        where ``h_all`` is the ``[B, S, NH*dv]`` buffer complete on every rank."""
+        from . import ops
+        self.barrier()   # peers are done reading the previous contents of their buffers
+        _, st = ops.mlstm_chunkwise(q, k, v, i, f, state, workspace=workspace, h_out=self.h_view,
+                                    h_peer_ptrs=self.peer_ptrs)
+        self.barrier()   # every rank's kernel has finished: all slots of all buffers are written
+        h_all = self.buf.view(self.B, self.S, self.NH * self.dv)
+        return (h_all if out_proj is None else h_all @ out_proj), st
+
+
+__all__ = ["head_range", "batch_range", "shard_heads", "all_gather_heads", "head_sharded_prefill", "FusedHeadGather"]
