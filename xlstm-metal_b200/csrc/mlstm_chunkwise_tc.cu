@@ -19,10 +19,9 @@
 // them to caller-provided scratch.
 //
 // Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc), warp 2 TMA stores of h,
-// warps 4-7 gate matrix P, then the C pass for rows [128,256) of C;
-// warps 8-11 Q~ scaling and q.n for the first half of the dqk boxes;
-// warps 12-15 K~ scaling, then the C pass for rows [0,128) (refresh Cb);
-// warps 16-19 Q~ for the other boxes, normaliser update, H epilogue.
+// warps 4-7 gate matrix P, then q~.n, then the C pass for rows [128,256) of C;
+// warps 8-11 Q~ scaling; warps 12-15 K~ scaling, then the C pass for rows [0,128) (refresh Cb);
+// warps 16-19 normaliser update (column sums of K~) and the H epilogue.
 // MMA issue order per tile: S, state update, P V, read-out (the update only needs the short K~
 // pass and frees K for the next tile's load while the longer Q~ pass still runs).
 // C is held in TMEM as C~ = C e^{-rho}: rho absorbs the per-tile decay, so the accumulator is not
@@ -198,13 +197,13 @@ template <int DQK> struct Smem {
     static constexpr uint32_t N_VEC = SMALL;               // float[DQK]   normaliser n
     static constexpr uint32_t QN = N_VEC + DQK * 4;        // float[LT]    q . n of the current tile
     static constexpr uint32_t INV = QN + LT * 4;           // float[2][LT] row sums of P, by tile parity
-    static constexpr uint32_t BARS = INV + 2 * LT * 4;     // uint64[16]
-    static constexpr uint32_t MISC = BARS + 16 * 8;        // tmem base, abort flag
+    static constexpr uint32_t BARS = INV + 2 * LT * 4;     // uint64[24]
+    static constexpr uint32_t MISC = BARS + 24 * 8;        // tmem base, abort flag
     static constexpr uint32_t TOTAL = MISC + 16;
 };
 
 enum { B_QFULL = 0, B_KFULL, B_VFULL, B_SDONE, B_H1DONE, B_UPDDONE, B_H2DONE, B_QSCALED, B_KSCALED, B_CBREADY,
-       B_PREADY, B_HFREE, B_NDONE, B_KREAD, B_HSTAGED, B_VFREE, B_NBARS };
+       B_PREADY, B_HFREE, B_NDONE, B_KREAD, B_HSTAGED, B_VFREE, B_QNDONE, B_NBARS };
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -215,19 +214,31 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&v);
 }
+// x * w for a packed pair of bf16, w = whi + wlo given as two packed bf16 pairs: rn(x*whi + rn(x*wlo)).
+// Within 2^-16 of the correctly rounded product with the fp32 factor, at 2 instructions per pair.
+__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t x, uint32_t whi2, uint32_t wlo2) {
+    const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162 *>(&x);
+    const __nv_bfloat162 r = __hfma2(xv, *reinterpret_cast<const __nv_bfloat162 *>(&whi2),
+                                     __hmul2(xv, *reinterpret_cast<const __nv_bfloat162 *>(&wlo2)));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+__device__ __forceinline__ void split_scale(float w, uint32_t &whi2, uint32_t &wlo2) {
+    const float hi = __bfloat162float(__float2bfloat16_rn(w));
+    whi2 = pack_bf16(hi, hi);
+    wlo2 = pack_bf16(w - hi, w - hi);
+}
 __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
     return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
 }
 
-// Q~ = Q * rowscale in place for boxes [q_begin, q_end) of the Q tile, and the partial q . n of those
-// columns added to s_qn.  Lane mapping: lane = (g, c) with c the physical 16-byte chunk and g a row
-// group; a warp owns the rows with (row & 7) in {2w, 2w+1}, so for a fixed residue rho every lane
-// always meets the same LOGICAL chunk c ^ rho: its 8 values of n stay in registers for 4 rows and the
-// tile loads are 4 x 128 contiguous bytes per instruction (no bank conflicts).
-template <int DQK, int QB, int QE>
-__device__ __forceinline__ void q_pass_boxes(unsigned char *smem, const float *s_n, float *s_qn, const float (&w2)[2][4],
-                                             int wl, int lane) {
+// q~ . n for all rows of the (already scaled) Q~ tile, added to s_qn.  Lane mapping: lane = (g, c) with
+// c the physical 16-byte chunk and g a row group; a warp owns the rows with (row & 7) in {2w, 2w+1}, so
+// for a fixed residue rho every lane always meets the same LOGICAL chunk c ^ rho: its 8 values of n are
+// loaded once per (rho, box) and the tile loads are 4 x 128 contiguous bytes per instruction.
+template <int DQK>
+__device__ __forceinline__ void qn_pass(const unsigned char *smem, const float *s_n, float *s_qn, int wl, int lane) {
     using SM = Smem<DQK>;
+    constexpr int NBOX = SM::NBOX;
     const int c = lane & 7, g = lane >> 3;
     float part[2][4];
 #pragma unroll
@@ -237,24 +248,17 @@ __device__ __forceinline__ void q_pass_boxes(unsigned char *smem, const float *s
 #pragma unroll
         for (int i = 0; i < 4; ++i) part[rr][i] = 0.f;
 #pragma unroll
-        for (int q = QB; q < QE; ++q) {
+        for (int q = 0; q < NBOX; ++q) {
             const float *np = s_n + q * 64 + ((c ^ rho) << 3);
             const float4 na = *reinterpret_cast<const float4 *>(np);
             const float4 nb = *reinterpret_cast<const float4 *>(np + 4);
-            unsigned char *base = smem + SM::Q + q * SM::BOX + row0 * 128 + (c << 4);
-            uint4 v[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v[i] = *reinterpret_cast<const uint4 *>(base + i * 32 * 128);
+            const unsigned char *base = smem + SM::Q + q * SM::BOX + row0 * 128 + (c << 4);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float2 f0 = unpack_bf16(v[i].x), f1 = unpack_bf16(v[i].y);
-                const float2 f2 = unpack_bf16(v[i].z), f3 = unpack_bf16(v[i].w);
+                const uint4 v = *reinterpret_cast<const uint4 *>(base + i * 32 * 128);
+                const float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
                 part[rr][i] += (f0.x * na.x + f0.y * na.y + f1.x * na.z + f1.y * na.w) +
                                (f2.x * nb.x + f2.y * nb.y + f3.x * nb.z + f3.y * nb.w);
-                const float w = w2[rr][i];   // fp32 scale, one rounding of the product
-                v[i].x = pack_bf16(f0.x * w, f0.y * w); v[i].y = pack_bf16(f1.x * w, f1.y * w);
-                v[i].z = pack_bf16(f2.x * w, f2.y * w); v[i].w = pack_bf16(f3.x * w, f3.y * w);
-                *reinterpret_cast<uint4 *>(base + i * 32 * 128) = v[i];
             }
         }
     }
@@ -266,19 +270,31 @@ __device__ __forceinline__ void q_pass_boxes(unsigned char *smem, const float *s
             v += __shfl_xor_sync(0xffffffffu, v, 1);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
             v += __shfl_xor_sync(0xffffffffu, v, 4);
-            if (c == 0) atomicAdd(s_qn + (2 * wl + rr) + 8 * g + 32 * i, v);
+            if (c == 0) s_qn[(2 * wl + rr) + 8 * g + 32 * i] = v;
         }
 }
 
-// the row scales of the 8 rows a lane of the Q~ pass owns
-__device__ __forceinline__ void q_pass_scales(const float *winq_g, int wl, int lane, float (&w2)[2][4]) {
-    const int g = lane >> 3;
+// In-place row scaling of a [128 x DQK] bf16 tile (boxes of 64 columns, 128-byte swizzle): thread = row,
+// 16-byte chunks visited in a rotated order so that the 8 lanes of a quarter-warp hit 8 different banks.
+template <int DQK>
+__device__ __forceinline__ void scale_rows(unsigned char *tile, int row, float w) {
+    using SM = Smem<DQK>;
+    uint32_t whi, wlo;
+    split_scale(w, whi, wlo);
+#pragma unroll 2
+    for (int q = 0; q < SM::NBOX; ++q) {
+        unsigned char *rowp = tile + q * SM::BOX + row * 128;
+        uint4 v[8];
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr)
+        for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(rowp + (((c + row) & 7) << 4));
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            w2[rr][i] = winq_g[(2 * wl + rr) + 8 * g + 32 * i];
+        for (int c = 0; c < 8; ++c) {
+            v[c].x = scale_bf16x2(v[c].x, whi, wlo); v[c].y = scale_bf16x2(v[c].y, whi, wlo);
+            v[c].z = scale_bf16x2(v[c].z, whi, wlo); v[c].w = scale_bf16x2(v[c].w, whi, wlo);
         }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(rowp + (((c + row) & 7) << 4)) = v[c];
+    }
 }
 
 // One 128-row half of the initial state: global fp32 -> Cb (bf16, swizzled MN-major) and TMEM
@@ -387,13 +403,12 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         mbar_init(&bars[B_QFULL], 1);   mbar_init(&bars[B_KFULL], 1);   mbar_init(&bars[B_VFULL], 1);
         mbar_init(&bars[B_SDONE], 1);   mbar_init(&bars[B_H1DONE], 1);  mbar_init(&bars[B_UPDDONE], 1);
         mbar_init(&bars[B_H2DONE], 1);
-        mbar_init(&bars[B_QSCALED], 256); mbar_init(&bars[B_KSCALED], 128); mbar_init(&bars[B_CBREADY], 128 * NHALF);
+        mbar_init(&bars[B_QSCALED], 128); mbar_init(&bars[B_KSCALED], 128); mbar_init(&bars[B_CBREADY], 128 * NHALF);
         mbar_init(&bars[B_PREADY], 128);  mbar_init(&bars[B_HFREE], 128);   mbar_init(&bars[B_NDONE], 128);  mbar_init(&bars[B_KREAD], 128);
-        mbar_init(&bars[B_HSTAGED], 128); mbar_init(&bars[B_VFREE], 1);
+        mbar_init(&bars[B_HSTAGED], 128); mbar_init(&bars[B_VFREE], 1); mbar_init(&bars[B_QNDONE], 128);
         mbar_fence_init();
         tma_prefetch_desc(&p.tq); tma_prefetch_desc(&p.tk); tma_prefetch_desc(&p.tv);
     }
-    if (tid < LT) s_qn[tid] = 0.f;   // q . n is accumulated with shared-memory atomics by two warpgroups
     if (warp == 1) tmem_alloc(tmem_slot, 512);
     tc_fence_before_sync();
     __syncthreads();
@@ -415,7 +430,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 TRACE(17);
                 mbar_expect_tx(&bars[B_KFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::K + q * SM::BOX, &p.tk, &bars[B_KFULL], q * 64, t0, hd, b);
-                if (k > 0 && !mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag)) break;
+                if (k > 0 && !(mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag) &&
+                               mbar_wait(&bars[B_QNDONE], (k - 1) & 1, abort_flag))) break;
                 TRACE(16);
                 mbar_expect_tx(&bars[B_QFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[B_QFULL], q * 64, t0, hd, b);
@@ -555,6 +571,13 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             tc_fence_before_sync();
             mbar_arrive(&bars[B_PREADY]);
             if (t == 0) TRACE(6);
+            // q~ . n (the state part of the normaliser) from the scaled tile Q~ and the previous n:
+            // needs Q~ complete, n of the previous tile final, and the previous epilogue done with s_qn
+            if (!mbar_wait(&bars[B_QSCALED], ph, abort_flag)) break;
+            if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
+            if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
+            qn_pass<DQK>(smem, s_n, s_qn, warp - 4, lane);
+            mbar_arrive(&bars[B_QNDONE]);
             if (NHALF == 2) {  // C pass for rows [128,256) of C (the K~ warps take rows [0,128))
                 const bool last = (k == NCH - 1);
                 if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
@@ -570,19 +593,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             }
         }
     } else if (warp >= 8 && warp < 12) {
-        // ================= Q~ = Q * e^{m-x_t} dqk^-1/2 in place and q . n: first half of the boxes ==========
+        // ================= Q~ = Q * e^{m-x_t+rho} dqk^-1/2 in place =================
         const int t = tid - 256;
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
-            float w2[2][4];
-            q_pass_scales(gbase + (size_t)k * GW + G_WINQ, warp - 8, lane, w2);
+            const float winq = gbase[(size_t)k * GW + G_WINQ + t];
             if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
-            // n of the previous tile complete (tile 0: written by the prologue); the previous epilogue has
-            // read and cleared s_qn (it arrives on HFREE afterwards)
-            if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
-            if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
             if (t == 0) TRACE(9);
-            q_pass_boxes<DQK, 0, NBOX / 2>(smem, s_n, s_qn, w2, warp - 8, lane);
+            scale_rows<DQK>(smem + SM::Q, t, winq);
             if (t == 0) TRACE(10);
             fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor-core (async) proxy
             mbar_arrive(&bars[B_QSCALED]);
@@ -611,22 +629,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             const float decay_next = last ? g[G_SCAL + 2] : g[GW + G_SCAL + 0];
             if (!(mbar_wait(&bars[B_KFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
             if (r == 0) TRACE(12);
-#pragma unroll 1
-            for (int q = 0; q < NBOX; ++q) {
-                unsigned char *rowp = smem + SM::K + q * SM::BOX + r * 128;
-                uint4 v[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(rowp + (((c + r) & 7) << 4));
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float2 f0 = unpack_bf16(v[c].x), f1 = unpack_bf16(v[c].y);
-                    const float2 f2 = unpack_bf16(v[c].z), f3 = unpack_bf16(v[c].w);
-                    v[c].x = pack_bf16(f0.x * w, f0.y * w); v[c].y = pack_bf16(f1.x * w, f1.y * w);
-                    v[c].z = pack_bf16(f2.x * w, f2.y * w); v[c].w = pack_bf16(f3.x * w, f3.y * w);
-                }
-#pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(rowp + (((c + r) & 7) << 4)) = v[c];
-            }
+            scale_rows<DQK>(smem + SM::K, r, w);
             fence_proxy_async_smem();
             mbar_arrive(&bars[B_KSCALED]);
             if (r == 0) TRACE(13);
@@ -645,7 +648,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             }
         }
     } else if (warp >= 16) {
-        // ===== second half of the Q~ boxes; normaliser update n' = decay n + colsum(K~); H epilogue =====
+        // ===== normaliser update n' = decay n + colsum(K~); H epilogue =====
         const int r = tid - 512;                         // token row of H = TMEM lane
         const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
         for (int k = 0; k < NCH; ++k) {
@@ -653,15 +656,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             const float *g = gbase + (size_t)k * GW;
             const float decay = g[G_SCAL + 0];
             const bool last = (k == NCH - 1);
-            float w2[2][4];
-            q_pass_scales(g + G_WINQ, warp - 16, lane, w2);
-            if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
-            if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
-            if (r == 0) TRACE(19);
-            q_pass_boxes<DQK, NBOX / 2, NBOX>(smem, s_n, s_qn, w2, warp - 16, lane);
-            if (r == 0) TRACE(20);
-            fence_proxy_async_smem();
-            mbar_arrive(&bars[B_QSCALED]);
             // column sums of K~
             if (!mbar_wait(&bars[B_KSCALED], ph, abort_flag)) break;
             if (r == 0) TRACE(22);
@@ -684,8 +678,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             }
             if (r == 0) TRACE(21);
             mbar_arrive(&bars[B_KREAD]);   // K~ no longer read by the CUDA cores: the tile may be reloaded
-            // n is rewritten only after every q . n of this tile has been taken
-            if (!mbar_wait(&bars[B_QSCALED], ph, abort_flag)) break;
+            // n is rewritten only after q~ . n of this tile has been taken
+            if (!mbar_wait(&bars[B_QNDONE], ph, abort_flag)) break;
             if (q < NBOX) {
                 const int j = q * 64 + cp * 2;
                 const float n0v = decay * s_n[j] + s0, n1v = decay * s_n[j + 1] + s1;
@@ -702,9 +696,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                   mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
             tc_fence_after_sync();
             if (r == 0) TRACE(7);
-            const float winq = g[G_WINQ + r];
-            const float den = s_qn[r] * winq + s_rs[ph * LT + r];
-            s_qn[r] = 0.f;
+            const float den = s_qn[r] + s_rs[ph * LT + r];   // q~ . n already carries the row scale
             const float inv = 1.0f / (fmaxf(fabsf(den), g[G_EMT + r]) + p.eps);
             // H -> bf16 h tile staged in the (now idle) V buffer, in the swizzled box layout of the h
             // tensor maps; one thread then issues TMA stores to this GPU's h and to every peer's buffer
