@@ -529,25 +529,39 @@ def run_model(torch, device, prompt_len, new_tokens):
     ids = torch.randint(0, 50304, (1, prompt_len), generator=g)
     runner.forward(ids[:, :256])  # warm-up (kernels, cuBLAS handles)
     runner.reset_state()
-    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     torch.cuda.synchronize()
     e[0].record()
     logits = runner.forward(ids)
     tok = int(logits[0, -1].argmax())
     e[1].record()
-    out = []
-    for _ in range(new_tokens):
-        out.append(tok)
-        tok = runner.generate_next_token(torch.tensor([[tok]]), temperature=0.0)
-    e[2].record()
+    out = [tok]
+    tok = runner.generate_next_token(torch.tensor([[tok]]), temperature=0.0)   # eager step; the next call captures
+    out.append(tok)
+    tok = int(runner._decode_step_graph(tok).argmax())                          # builds the decode graph (untimed)
+    out.append(tok)
     torch.cuda.synchronize()
-    pre_ms, dec_ms = e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+    e[2].record()
+    for _ in range(new_tokens):
+        tok = int(runner._decode_step_graph(tok).argmax())
+        out.append(tok)
+    e[3].record()
+    torch.cuda.synchronize()
+    e_eager = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    e_eager[0].record()
+    for _ in range(16):
+        tok = runner.generate_next_token(torch.tensor([[tok]]), temperature=0.0)
+    e_eager[1].record()
+    torch.cuda.synchronize()
+    eager_ms = e_eager[0].elapsed_time(e_eager[1]) / 16
+    pre_ms, dec_ms = e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])
     n_params = sum(p.numel() for p in runner.model.parameters())
     del runner
     torch.cuda.empty_cache()
     return {"workload": f"xLSTM-7B-shaped random init, B=1, prompt {prompt_len} + {new_tokens} greedy tokens, bf16 (BASELINE configs[2])",
             "params": n_params, "prefill_ms": pre_ms, "prefill_tokens_per_s": prompt_len / (pre_ms * 1e-3),
             "decode_ms_per_token": dec_ms / new_tokens, "decode_tokens_per_s": new_tokens / (dec_ms * 1e-3),
+            "decode": "CUDA-graph replay of the single-token step", "decode_eager_ms_per_token": eager_ms,
             "note": "GEMM-bound context number (cuBLAS via torch); the mLSTM cell is ~1 % of prefill FLOPs"}
 
 

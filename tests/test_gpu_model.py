@@ -75,6 +75,10 @@ def test_runner_generate_is_stateful_and_greedy(tiny_model, golden):
     out = runner.generate(prompt, max_tokens=6, temperature=0.0)
     assert out[:40] == prompt and len(out) == 46
     assert runner.generate(prompt, max_tokens=6, temperature=0.0) == out  # state reset between calls
+    # decode steps replayed as a CUDA graph give the same tokens (twice: the second call reuses the graph)
+    assert runner.generate(prompt, max_tokens=6, temperature=0.0, use_cuda_graph=True) == out
+    assert runner.generate(prompt[:17], max_tokens=5, temperature=0.0, use_cuda_graph=True) == \
+        runner.generate(prompt[:17], max_tokens=5, temperature=0.0)
     # the same tokens from the full-sequence logits of the reference fixture's weights
     with torch.inference_mode():
         seq = torch.tensor([out[:-1]])

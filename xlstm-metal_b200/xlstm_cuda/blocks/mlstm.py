@@ -87,12 +87,15 @@ class mLSTMRecurrentKernelCell(_KernelCellBase):
     def __init__(self, num_heads: int, qk_dim_per_head: int, v_dim_per_head: int, eps: float = 1e-6,
                  compute_dtype: torch.dtype = torch.float32, state_dtype: torch.dtype = torch.float32):
         super().__init__(num_heads, qk_dim_per_head, v_dim_per_head, eps, compute_dtype, state_dtype)
+        # True: a single-token step overwrites the caller's C instead of returning a new tensor (the
+        # reference always returns new tensors; the runner switches this on for graph-captured decode)
+        self.inplace_state = False
 
     def forward(self, q, k, v, i_preact, f_preact, state: Optional[State] = None):
         q, k, v, i_preact, f_preact = self._cast_in(q, k, v, i_preact, f_preact)
         if q.shape[2] == 1:
             h, st = ops.mlstm_step(q[:, :, 0], k[:, :, 0], v[:, :, 0], i_preact[:, :, 0], f_preact[:, :, 0],
-                                   state, self.eps)
+                                   state, self.eps, inplace=self.inplace_state)
             return h.unsqueeze(2), self._cast_state(st)
         h, st = ops.mlstm_chunkwise(q, k, v, i_preact, f_preact, state, 64, self.eps)
         return h, self._cast_state(st)

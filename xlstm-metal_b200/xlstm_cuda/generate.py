@@ -50,6 +50,7 @@ class xLSTMRunner:
                                 norm_reduce_force_float32=self.norm_reduce_force_float32, device=device)
         self.model.eval()
         self.state = None
+        self._graph = None          # captured single-token decode step (see _decode_step_graph)
         self.tokenizer = None
         if (self.model_path / "tokenizer.json").exists():
             from tokenizers import Tokenizer
@@ -63,6 +64,59 @@ class xLSTMRunner:
 
     def reset_state(self) -> None:
         self.state = None
+
+    # ---- graph-captured decode ------------------------------------------------------------------
+    # A decode step of a 32-block model is ~700 small launches; replaying them as one CUDA graph removes
+    # the per-launch host cost.  The graph works on static buffers: one token id, the per-block state
+    # (C updated in place by the step kernel, n and m copied back) and the soft-capped logits.
+    def _set_inplace(self, flag: bool) -> None:
+        for blk in self.model.blocks:
+            cell = getattr(getattr(blk, "mlstm_cell", None), "recurrent_kernel", None)
+            if cell is not None:
+                cell.inplace_state = flag
+
+    def _eager_static_step(self) -> torch.Tensor:
+        logits, new_state = self.model(self._g_ids, self._g_state, return_last_states=True)
+        for old, new in zip(self._g_state, new_state):
+            for o, n_ in zip(old, new):
+                if n_ is not o:
+                    o.copy_(n_)
+        return soft_cap(logits, self.output_logit_soft_cap)
+
+    def _build_decode_graph(self) -> None:
+        dev = self.model.device
+        self._g_ids = torch.zeros(1, 1, dtype=torch.long, device=dev)
+        self._g_state = [tuple(t.detach().clone().contiguous() for t in st) for st in self.state]
+        saved = [tuple(t.clone() for t in st) for st in self._g_state]
+        self._set_inplace(True)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.inference_mode():
+            for _ in range(2):            # warm-up outside capture (allocator, cuBLAS handles)
+                self._eager_static_step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.inference_mode(), torch.cuda.graph(graph):
+            self._g_logits = self._eager_static_step()
+        self._set_inplace(False)
+        for st, sv in zip(self._g_state, saved):   # the warm-up and capture steps advanced the state: restore it
+            for t, v in zip(st, sv):
+                t.copy_(v)
+        self._graph = graph
+
+    @torch.inference_mode()
+    def _decode_step_graph(self, token: int) -> torch.Tensor:
+        """Logits ``[vocab]`` for one more token, through the captured graph (state carried in place)."""
+        if self._graph is None:
+            self._build_decode_graph()
+        elif self.state is not self._g_state:     # a new sequence: load its state into the static buffers
+            for st, new in zip(self._g_state, self.state):
+                for t, v in zip(st, new):
+                    t.copy_(v)
+        self.state = self._g_state
+        self._g_ids.fill_(int(token))
+        self._graph.replay()
+        return self._g_logits[0, -1, :]
 
     @torch.inference_mode()
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
@@ -91,7 +145,7 @@ class xLSTMRunner:
 
     def generate(self, prompt: Union[str, Sequence[int], torch.Tensor], max_tokens: int = 50, temperature: float = 1.0,
                  top_k: Optional[int] = None, top_p: Optional[float] = None,
-                 stop_tokens: Optional[List[int]] = None) -> Union[str, List[int]]:
+                 stop_tokens: Optional[List[int]] = None, use_cuda_graph: bool = False) -> Union[str, List[int]]:
         as_text = isinstance(prompt, str)
         if as_text:
             if self.tokenizer is None:
@@ -102,8 +156,11 @@ class xLSTMRunner:
         self.reset_state()
         generated = list(tokens)
         current = torch.tensor([tokens], dtype=torch.long)
-        for _ in range(max_tokens):
-            token = self.generate_next_token(current, temperature=temperature, top_k=top_k, top_p=top_p)
+        for step in range(max_tokens):
+            if use_cuda_graph and step > 0 and temperature == 0.0:
+                token = int(torch.argmax(self._decode_step_graph(generated[-1])).item())   # greedy, graph replay
+            else:
+                token = self.generate_next_token(current, temperature=temperature, top_k=top_k, top_p=top_p)
             generated.append(token)
             if stop and token in stop:
                 break
