@@ -167,6 +167,69 @@ int xlstm_slstm_recurrent(const void *gx, const void *R, const float *rb,
                           void *hs, float *c1, float *n1, float *h1, float *m1,
                           int B, int S, int NH, int dh, float cap, int dtype, void *stream);
 
+/*
+ * ---- the callers either side of the cells: norm, output epilogue, FFN gate, causal convolution ----
+ * One pass over HBM each, 16-byte accesses, fp32 math, one rounding to `dtype` on the way out.
+ */
+
+/*
+ * RMSNorm over the last dimension of x [rows, cols]:
+ *   y = x * rsqrt(mean(x^2) + eps) * w      (w: [cols] in `dtype`, or NULL for no weight).
+ * y may alias x.
+ * Replaces rms_norm_forward(x2d, weight, eps) -> Tensor
+ * (xlstm_metal/torch_native/blocks/rms_norm/rms_norm_extension.mm:61-105, kernel
+ *  rms_norm_kernel.metal:11-31; Python entry rmsnorm.py:30-40).
+ */
+int xlstm_rms_norm(const void *x, const void *w, void *y, int64_t rows, int cols, float eps, int dtype, void *stream);
+
+/*
+ * Residual add fused into the norm that follows it: sum = x + r (rounded to `dtype`, the new residual
+ * stream), y = RMSNorm(sum) * w.  sum may alias x or r.  Replaces the pair
+ * `x = x + mlstm_out; x_normed = self.norm_ffn(x)` of mLSTMBlock.forward
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_block.py:192-198) and of sLSTMBlock.forward
+ * (.../slstm/slstm_block.py:101-131).
+ */
+int xlstm_add_rms_norm(const void *x, const void *r, const void *w, void *sum, void *y, int64_t rows, int cols,
+                       float eps, int dtype, void *stream);
+
+/*
+ * mLSTM output epilogue in one pass:
+ *   y[b,s,head*dv+j] = h[b,head,s,j] / sqrt(mean_j(h^2) + eps) * w[head*dv+j] * sigmoid(ogate[b,s,head*dv+j]).
+ * h: [B,NH,S,dv] with element strides h_strides = (batch, head, token), innermost contiguous (NULL = dense);
+ * ogate: [B*S rows, NH*dv] with leading dimension ogate_ld elements (0 = dense), so it may be a column block
+ * of a fused projection output; y: [B,S,NH*dv] dense; w: [NH*dv] or NULL.  dv, the strides and ogate_ld
+ * must be multiples of 16 bytes.
+ * Replaces the per-head norm, sigmoid and product of mLSTMOutputCell.forward
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/mlstm_output_cell.py:84-94) with
+ * MultiHeadRMSNorm.forward (.../multihead_norm/multihead_norm.py:43-64).
+ */
+int xlstm_mlstm_output_gate(const void *h, const void *ogate, const void *w, void *y, int B, int NH, int S, int dv,
+                            const int64_t *h_strides, int64_t ogate_ld, float eps, int dtype, void *stream);
+
+/*
+ * SwiGLU gate: y[r,c] = silu(g[r,c]) * u[r,c] for r < rows, c < cols.  g and u have leading dimensions
+ * ldg, ldu (elements), so they may be the two column blocks of one fused GEMM output; y is dense.
+ * Replaces F.silu(gate) * up in mLSTMBlock.forward
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_block.py:198-204).
+ */
+int xlstm_swiglu(const void *g, const void *u, void *y, int64_t rows, int cols, int64_t ldg, int64_t ldu, int dtype,
+                 void *stream);
+
+/*
+ * Causal depthwise convolution over tokens, channels last, optional SiLU:
+ *   y[b,s,c] = act(bias[c] + sum_{j<K} w[c,j] * x[b, s-(K-1)+j, c]),   K <= 8.
+ * x, y: [B,S,C]; w: [C,K] (the [C,1,K] weight of a depthwise nn.Conv1d); bias: [C] or NULL.
+ * Tokens before the first one are taken from state_in [B,K-1,C] (oldest first; NULL = zeros, which is
+ * what the reference does on every call); state_out (or NULL) receives the last K-1 inputs and may
+ * alias state_in when S <= 16 (single-token decode).
+ * Replaces causal_conv1d_depthwise(x_seq, weight, bias) -> Tensor
+ * (xlstm_metal/torch_native/blocks/slstm/slstm_layers/causal_conv1d/causal_conv_extension.mm:114-164,
+ *  depthwise_kernel.metal:12-44) in the tap order of the nn.Conv1d path (causal_conv1d.py:61-67), and
+ * the SiLU that follows it (slstm_projection_cell.py:110-117).
+ */
+int xlstm_causal_conv1d(const void *x, const void *w, const void *bias, const void *state_in, void *state_out,
+                        void *y, int B, int S, int C, int K, int act_silu, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

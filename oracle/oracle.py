@@ -96,6 +96,38 @@ def multihead_rmsnorm(x, w, eps: float):
     return y.reshape(*x.shape[:-2], NH * DH)
 
 
+def mlstm_output_gate(h, og, w, eps: float):
+    """h: [B,NH,S,dv]; og: [B,S,NH*dv]; w: [NH*dv] or None -> [B,S,NH*dv]."""
+    h, og = _c(h), _c(og)
+    w = None if w is None else _c(w)
+    B, NH, S, dv = h.shape
+    y = np.empty((B, S, NH * dv), dtype=np.float32)
+    lib().xo_mlstm_output_gate(_p(h), _p(og), _p(w), _p(y), ctypes.c_int(B), ctypes.c_int(NH), ctypes.c_int(S),
+                               ctypes.c_int(dv), ctypes.c_float(eps))
+    return y
+
+
+def swiglu(g, u):
+    g, u = _c(g), _c(u)
+    y = np.empty_like(g)
+    lib().xo_swiglu(_p(g), _p(u), _p(y), ctypes.c_long(g.size))
+    return y
+
+
+def causal_conv1d(x, w, bias=None, state=None, silu: bool = False, return_state: bool = False):
+    """x: [B,S,C]; w: [C,K]; bias: [C]; state: [B,K-1,C] (inputs before the first token)."""
+    x, w = _c(x), _c(w)
+    bias = None if bias is None else _c(bias)
+    state = None if state is None else _c(state)
+    B, S, C = x.shape
+    K = w.shape[-1]
+    y = np.empty_like(x)
+    st = np.empty((B, K - 1, C), dtype=np.float32) if return_state else None
+    lib().xo_causal_conv1d(_p(x), _p(w), _p(bias), _p(state), _p(st), _p(y), ctypes.c_int(B), ctypes.c_int(S),
+                           ctypes.c_int(C), ctypes.c_int(K), ctypes.c_int(1 if silu else 0))
+    return (y, st) if return_state else y
+
+
 def _mlstm_common(fn, q, k, v, i, f, state, eps, *tail):
     q, k, v, i, f = map(_c, (q, k, v, i, f))
     B, NH, S, dqk = q.shape

@@ -119,6 +119,65 @@ void xo_multihead_rmsnorm(const float *x, const float *w, float *y, long rows, i
     }
 }
 
+/*
+ * mLSTM output epilogue (mlstm_output_cell.py:84-94 with multihead_norm.py:43-64):
+ * h: [B,NH,S,dv]  og (output-gate pre-activation), y: [B,S,NH*dv]  w: flat [NH*dv] or NULL
+ *   y[b,s,head*dv+j] = h[b,head,s,j] / sqrt(mean_j h^2 + eps) * w[head*dv+j] * sigmoid(og[b,s,head*dv+j])
+ */
+void xo_mlstm_output_gate(const float *h, const float *og, const float *w, float *y, int B, int NH, int S, int dv,
+                          float eps) {
+#pragma omp parallel for schedule(static)
+    for (long r = 0; r < (long)B * S * NH; ++r) {
+        int head = (int)(r % NH);
+        long bs = r / NH, b = bs / S, s = bs % S;
+        const float *hr = h + ((b * NH + head) * S + s) * dv;
+        const float *ogr = og + r * dv;
+        float *yr = y + r * dv;
+        float ss = 0.f;
+        for (int j = 0; j < dv; ++j) ss += hr[j] * hr[j];
+        float rms = sqrtf(ss / (float)dv + eps);
+        for (int j = 0; j < dv; ++j)
+            yr[j] = (hr[j] / rms) * (w ? w[head * dv + j] : 1.0f) * (1.0f / (1.0f + expf(-ogr[j])));
+    }
+}
+
+/* SwiGLU gate, mlstm_block.py:198-204: y = silu(g) * u */
+void xo_swiglu(const float *g, const float *u, float *y, long n) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < n; ++i) y[i] = g[i] / (1.0f + expf(-g[i])) * u[i];
+}
+
+/*
+ * Causal depthwise conv over tokens, channels last (depthwise_kernel.metal:12-44 for the layout;
+ * tap order of the nn.Conv1d path, causal_conv1d.py:61-67: tap K-1 meets the current token):
+ *   y[b,s,c] = act(bias[c] + sum_j w[c,j] * x[b, s-(K-1)+j, c]);  tokens < 0 from state [B,K-1,C] or zero.
+ * state_out (or NULL): the last K-1 inputs of [state ; x].  act: 0 none, 1 SiLU (slstm_projection_cell.py:110-117).
+ */
+void xo_causal_conv1d(const float *x, const float *w, const float *bias, const float *state, float *state_out,
+                      float *y, int B, int S, int C, int K, int act) {
+    int H = K - 1;
+    for (int b = 0; b < B; ++b) {
+        for (int s = 0; s < S; ++s)
+            for (int c = 0; c < C; ++c) {
+                float acc = bias ? bias[c] : 0.0f;
+                for (int j = 0; j < K; ++j) {
+                    int t = s - H + j;
+                    float xv = t >= 0 ? x[((long)b * S + t) * C + c]
+                                      : (state ? state[((long)b * H + (H + t)) * C + c] : 0.0f);
+                    acc += w[(long)c * K + j] * xv;
+                }
+                y[((long)b * S + s) * C + c] = act ? acc / (1.0f + expf(-acc)) : acc;
+            }
+        if (state_out)
+            for (int j = 0; j < H; ++j)
+                for (int c = 0; c < C; ++c) {
+                    int t = S - H + j;
+                    state_out[((long)b * H + j) * C + c] =
+                        t >= 0 ? x[((long)b * S + t) * C + c] : (state ? state[((long)b * H + (H + t)) * C + c] : 0.0f);
+                }
+    }
+}
+
 /* ---- mLSTM recurrent sequence (the torch_native semantics of record) --- */
 /*
  * q,k: [B,NH,S,dqk]  v: [B,NH,S,dv]  ig,fg: [B,NH,S]

@@ -120,3 +120,41 @@ def test_slstm_block_diagonal(golden):
     for got, key in zip(st, "cnhm"):
         assert relerr(host(got), g[key]) < TOL
     assert relerr(host(y2), g["y2"]) < TOL and relerr(host(st2[0]), g["c2"]) < TOL
+
+
+def test_fused_projections_keep_names_values_and_results(tiny_model, golden):
+    """One GEMM for q,k,v,i,f,o and one for the FFN up projections: same parameters, same results."""
+    import copy
+    model, _ = tiny_model
+    g = golden("model_tiny_fp32")
+    fused = copy.deepcopy(model)
+    assert fused.fuse_projections() == len(fused.blocks)
+    assert list(fused.state_dict()) == list(model.state_dict())
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), fused.named_parameters()):
+        assert n1 == n2 and torch.equal(p1, p2)
+    blk = fused.blocks[0]
+    assert blk.mlstm_cell._fused_weights() is not None and blk._fused_ffn() is not None
+    ids = torch.from_numpy(g["ids"])
+    with torch.inference_mode():
+        logits, states = fused(ids, None, return_last_states=True)
+        assert relerr(host(logits), g["logits"]) < TOL
+        for i, (C, n, m) in enumerate(states):
+            assert relerr(host(C), g[f"C{i}"]) < TOL and relerr(host(n), g[f"n{i}"]) < TOL
+        # decode steps through the fused path (strided q,k,v,gate views of one GEMM output)
+        x = torch.from_numpy(g["block0_in"]).cuda()
+        s, ys = None, []
+        for t in range(6):
+            yt, s = blk(x[:, t:t + 1], s)
+            ys.append(yt)
+        assert relerr(host(torch.cat(ys, 1)), g["block0_out"][:, :6]) < TOL
+        # an in-place load after fusing lands in the fused matrices
+        blk.mlstm_cell.projection_cell.q_proj.weight.mul_(0.5)
+        assert blk.mlstm_cell._fused_weights() is not None
+        y_half, _ = blk(x, None)
+        assert relerr(host(y_half), g["block0_out"]) > 1e-3
+        # a dtype / device move detaches the views: the block falls back to the separate projections
+        moved = copy.deepcopy(model.blocks[0]).to(torch.float32)
+        moved.fuse_projections()
+        moved = moved.to("cuda:0", torch.float32)   # same dtype and device: storage is kept, still fused
+        y2, _ = moved(x, None)
+        assert relerr(host(y2), g["block0_out"]) < TOL

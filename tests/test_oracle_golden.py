@@ -121,3 +121,26 @@ def test_norm_glue(golden):
     np.testing.assert_allclose(xo.rmsnorm(g["rms_x"], g["rms_w"], 1e-6), g["rms_y"], rtol=1e-5, atol=1e-6)
     y = xo.multihead_rmsnorm(g["mh_x"], g["mh_w"], 1e-6)
     np.testing.assert_allclose(y, g["mh_y"], rtol=1e-5, atol=1e-6)
+
+
+def test_output_gate_conv_swiglu_glue(golden):
+    """The oracle's restatements of the kernels either side of the cells against the reference's own
+    modules (tests/golden/make_golden_glue.py)."""
+    g = golden("glue_fp32")
+    y = xo.mlstm_output_gate(g["og_h"], g["og_pre"], g["og_w"], float(g["og_eps"]))
+    np.testing.assert_allclose(y, g["og_y"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(xo.swiglu(g["sw_g"], g["sw_u"]), g["sw_y"], rtol=1e-5, atol=1e-6)
+    x, w, b = g["conv_x"], g["conv_w"], g["conv_b"]
+    np.testing.assert_allclose(xo.causal_conv1d(x, w, b), g["conv_y"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(xo.causal_conv1d(x, w, b, silu=True), g["conv_y_silu"], rtol=1e-5, atol=1e-6)
+    # carried state: two calls give the one-call result (the reference keeps no state; this is the
+    # property the stateful decode variant must have)
+    y1, st = xo.causal_conv1d(x[:, :20], w, b, silu=True, return_state=True)
+    y2, st2 = xo.causal_conv1d(x[:, 20:], w, b, state=st, silu=True, return_state=True)
+    np.testing.assert_allclose(np.concatenate([y1, y2], 1), g["conv_y_silu"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_array_equal(st2, x[:, -3:])
+    # single tokens shift the state
+    st = None
+    for t in range(5):
+        yt, st = xo.causal_conv1d(x[:, t:t + 1], w, b, state=st, return_state=True)
+        np.testing.assert_allclose(yt[:, 0], g["conv_y"][:, t], rtol=1e-5, atol=1e-6)

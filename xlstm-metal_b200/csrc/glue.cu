@@ -1,0 +1,445 @@
+// The elementwise / row-reduction kernels on either side of the recurrent cells: RMSNorm, the mLSTM
+// output epilogue (per-head RMS norm x weight x sigmoid(output gate)), the SwiGLU gate and the causal
+// depthwise convolution of the sLSTM projection.  All are single-pass and HBM-bound: every input is
+// read once with 16-byte accesses, reductions and math in fp32, one rounding on the way out.
+#include "common.cuh"
+
+namespace xl {
+
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T> __device__ __forceinline__ void ld16(const T *p, float *f);
+template <> __device__ __forceinline__ void ld16<float>(const float *p, float *f) {
+    const float4 a = *reinterpret_cast<const float4 *>(p);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+}
+template <> __device__ __forceinline__ void ld16<__nv_bfloat16>(const __nv_bfloat16 *p, float *f) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+template <typename T> __device__ __forceinline__ void st16(T *p, const float *f);
+template <> __device__ __forceinline__ void st16<float>(float *p, const float *f) {
+    *reinterpret_cast<float4 *>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void st16<__nv_bfloat16>(__nv_bfloat16 *p, const float *f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t *>(&v);
+    }
+    *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// ---------------------------------------------------------------------------
+// RMSNorm: one CTA per row, the row cached in registers (NV 16-byte vectors per thread)
+// ---------------------------------------------------------------------------
+constexpr int RN_THREADS = 128;
+
+// With a residual r: s = x + r is rounded to the activation type, written to `sum` (the new residual
+// stream) and the norm is taken of that rounded value, exactly as two separate ops would.
+template <typename T, int NV>
+__global__ void __launch_bounds__(RN_THREADS) rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ r,
+                                                              const T *__restrict__ w, T *__restrict__ sum,
+                                                              T *__restrict__ y, int cols, float eps) {
+    constexpr int VN = Vec16<T>::N;
+    __shared__ float s_part[RN_THREADS / 32];
+    const int nvec = cols / VN;
+    const T *xr = x + (size_t)blockIdx.x * cols;
+    T *yr = y + (size_t)blockIdx.x * cols;
+    float v[NV][VN];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int iv = threadIdx.x + i * RN_THREADS;
+        if (iv < nvec) {
+            ld16<T>(xr + (size_t)iv * VN, v[i]);
+            if (r) {
+                float rv[VN];
+                ld16<T>(r + (size_t)blockIdx.x * cols + (size_t)iv * VN, rv);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) v[i][e] += rv[e];
+                st16<T>(sum + (size_t)blockIdx.x * cols + (size_t)iv * VN, v[i]);
+                if (sizeof(T) == 2) {
+#pragma unroll
+                    for (int e = 0; e < VN; ++e) v[i][e] = __bfloat162float(__float2bfloat16_rn(v[i][e]));
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < VN; ++e) ss += v[i][e] * v[i][e];
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < RN_THREADS / 32; ++i) tot += s_part[i];
+    const float inv = rsqrtf(tot / (float)cols + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int iv = threadIdx.x + i * RN_THREADS;
+        if (iv < nvec) {
+            float wv[VN];
+            if (w) ld16<T>(w + (size_t)iv * VN, wv);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) v[i][e] = v[i][e] * inv * (w ? wv[e] : 1.0f);
+            st16<T>(yr + (size_t)iv * VN, v[i]);
+        }
+    }
+}
+
+// any width / alignment: two passes over the row (the second one hits L1/L2)
+template <typename T>
+__global__ void __launch_bounds__(RN_THREADS) rms_norm_generic_kernel(const T *__restrict__ x, const T *__restrict__ r,
+                                                                      const T *__restrict__ w, T *__restrict__ sum,
+                                                                      T *__restrict__ y, int cols, float eps) {
+    __shared__ float s_part[RN_THREADS / 32];
+    const T *xr = x + (size_t)blockIdx.x * cols;
+    T *yr = y + (size_t)blockIdx.x * cols;
+    float ss = 0.f;
+    if (r) {   // first pass also forms the new residual stream; later passes read it back
+        T *sr = sum + (size_t)blockIdx.x * cols;
+        for (int i = threadIdx.x; i < cols; i += RN_THREADS)
+            Elem<T>::st(sr + i, Elem<T>::ld(xr + i) + Elem<T>::ld(r + (size_t)blockIdx.x * cols + i));
+        __syncthreads();
+        xr = sr;
+    }
+    for (int i = threadIdx.x; i < cols; i += RN_THREADS) { const float a = Elem<T>::ld(xr + i); ss += a * a; }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < RN_THREADS / 32; ++i) tot += s_part[i];
+    const float inv = rsqrtf(tot / (float)cols + eps);
+    for (int i = threadIdx.x; i < cols; i += RN_THREADS)
+        Elem<T>::st(yr + i, Elem<T>::ld(xr + i) * inv * (w ? Elem<T>::ld(w + i) : 1.0f));
+}
+
+template <typename T>
+static int rms_norm_launch(const void *x, const void *r, const void *w, void *sum, void *y, int64_t rows, int cols,
+                           float eps, cudaStream_t st) {
+    constexpr int VN = Vec16<T>::N;
+    const T *xp = static_cast<const T *>(x), *rp = static_cast<const T *>(r), *wp = static_cast<const T *>(w);
+    T *sp = static_cast<T *>(sum), *yp = static_cast<T *>(y);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) |
+                           reinterpret_cast<uintptr_t>(r) | reinterpret_cast<uintptr_t>(sum)) & 15u) == 0 &&
+                         cols % VN == 0;
+    const int nvec = cols / VN;
+    const dim3 grid((unsigned)rows);
+    if (aligned && nvec <= RN_THREADS * 1) rms_norm_kernel<T, 1><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
+    else if (aligned && nvec <= RN_THREADS * 2) rms_norm_kernel<T, 2><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
+    else if (aligned && nvec <= RN_THREADS * 4) rms_norm_kernel<T, 4><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
+    else if (aligned && nvec <= RN_THREADS * 8) rms_norm_kernel<T, 8><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
+    else rms_norm_generic_kernel<T><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// mLSTM output epilogue: one warp per (batch, token, head) row of dv values
+// ---------------------------------------------------------------------------
+constexpr int OG_WARPS = 8;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(OG_WARPS * 32) mlstm_output_gate_kernel(
+    const T *__restrict__ h, const T *__restrict__ og, const T *__restrict__ w, T *__restrict__ y, int64_t rows, int NH,
+    int S, int dv, int64_t hsb, int64_t hsh, int64_t hss, int64_t ldo, float eps) {
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * OG_WARPS + (threadIdx.x >> 5);   // (b * S + s) * NH + head
+    if (row >= rows) return;
+    const int head = (int)(row % NH);
+    const int64_t bs = row / NH;
+    const int64_t b = bs / S, s = bs % S;
+    const T *hr = h + b * hsb + head * hsh + s * hss;
+    const int nvec = dv / VN;
+    float v[NV][VN];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int iv = lane + i * 32;
+        if (iv < nvec) {
+            ld16<T>(hr + (size_t)iv * VN, v[i]);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) ss += v[i][e] * v[i][e];
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+    const T *ogr = og + bs * ldo + (size_t)head * dv;
+    const T *wr = w ? w + (size_t)head * dv : nullptr;
+    T *yr = y + row * dv;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int iv = lane + i * 32;
+        if (iv < nvec) {
+            float o[VN], wv[VN];
+            ld16<T>(ogr + (size_t)iv * VN, o);
+            if (wr) ld16<T>(wr + (size_t)iv * VN, wv);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) v[i][e] = v[i][e] * inv * (wr ? wv[e] : 1.0f) * sigmoidf(o[e]);
+            st16<T>(yr + (size_t)iv * VN, v[i]);
+        }
+    }
+}
+
+template <typename T>
+static int output_gate_launch(const void *h, const void *og, const void *w, void *y, int B, int NH, int S, int dv,
+                              const int64_t *hs, int64_t ldo, float eps, cudaStream_t st) {
+    constexpr int VN = Vec16<T>::N;
+    const int nvec = dv / VN;
+    const int64_t rows = (int64_t)B * S * NH;
+    const unsigned grid = (unsigned)((rows + OG_WARPS - 1) / OG_WARPS);
+    const T *hp = static_cast<const T *>(h), *op = static_cast<const T *>(og), *wp = static_cast<const T *>(w);
+    T *yp = static_cast<T *>(y);
+    if (nvec <= 32) mlstm_output_gate_kernel<T, 1><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    else if (nvec <= 64) mlstm_output_gate_kernel<T, 2><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    else if (nvec <= 128) mlstm_output_gate_kernel<T, 4><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    else if (nvec <= 256) mlstm_output_gate_kernel<T, 8><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    else return XLSTM_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU gate: y[r, c] = silu(g[r, c]) * u[r, c]; g and u may be column blocks of one GEMM output
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_kernel(const T *__restrict__ g, const T *__restrict__ u, T *__restrict__ y,
+                                                     int64_t rows, int cols, int64_t ldg, int64_t ldu) {
+    constexpr int VN = Vec16<T>::N;
+    const int nvec = cols / VN;
+    const int64_t total = rows * nvec;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / nvec;
+        const int c = (int)(i % nvec) * VN;
+        float a[VN], b[VN];
+        ld16<T>(g + r * ldg + c, a);
+        ld16<T>(u + r * ldu + c, b);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) a[e] = silu(a[e]) * b[e];
+        st16<T>(y + r * cols + c, a);
+    }
+}
+
+template <typename T>
+__global__ void swiglu_scalar_kernel(const T *__restrict__ g, const T *__restrict__ u, T *__restrict__ y, int64_t rows,
+                                     int cols, int64_t ldg, int64_t ldu) {
+    const int64_t total = rows * cols;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t r = i / cols;
+        const int c = (int)(i % cols);
+        Elem<T>::st(y + i, silu(Elem<T>::ld(g + r * ldg + c)) * Elem<T>::ld(u + r * ldu + c));
+    }
+}
+
+template <typename T>
+static int swiglu_launch(const void *g, const void *u, void *y, int64_t rows, int cols, int64_t ldg, int64_t ldu,
+                         cudaStream_t st) {
+    constexpr int VN = Vec16<T>::N;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0 &&
+                         cols % VN == 0 && ldg % VN == 0 && ldu % VN == 0;
+    const int64_t work = aligned ? rows * (cols / VN) : rows * cols;
+    int64_t want = (work + 255) / 256;
+    const int grid = (int)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));
+    const T *gp = static_cast<const T *>(g), *up = static_cast<const T *>(u);
+    if (aligned) swiglu_kernel<T><<<grid, 256, 0, st>>>(gp, up, static_cast<T *>(y), rows, cols, ldg, ldu);
+    else swiglu_scalar_kernel<T><<<grid, 256, 0, st>>>(gp, up, static_cast<T *>(y), rows, cols, ldg, ldu);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// causal depthwise conv1d (+ SiLU), channels-last.  A thread owns VN adjacent channels and walks
+// CONV_T consecutive tokens with the last K-1 inputs in registers, so every input is read once
+// (plus a K-1 halo per token block); a warp covers 32*VN adjacent channels of one token.
+// ---------------------------------------------------------------------------
+constexpr int CONV_T = 16;
+constexpr int CONV_KMAX = 8;
+
+template <typename T, int K>
+__global__ void __launch_bounds__(128) causal_conv1d_kernel(const T *__restrict__ x, const T *__restrict__ w,
+                                                            const T *__restrict__ bias, const T *__restrict__ state_in,
+                                                            T *__restrict__ state_out, T *__restrict__ y, int S, int C,
+                                                            int act_silu) {
+    constexpr int VN = Vec16<T>::N;
+    const int cv = blockIdx.x * blockDim.x + threadIdx.x;   // channel vector
+    if (cv * VN >= C) return;
+    const int c0 = cv * VN;
+    const int b = blockIdx.z;
+    const int s_begin = blockIdx.y * CONV_T;
+    const int s_end = min(S, s_begin + CONV_T);
+    const T *xb = x + (size_t)b * S * C + c0;
+    T *yb = y + (size_t)b * S * C + c0;
+    constexpr int H = K - 1;                               // history length
+    float wk[K][VN];                                       // wk[j][e]: tap j of channel c0 + e
+#pragma unroll
+    for (int e = 0; e < VN; ++e)
+#pragma unroll
+        for (int j = 0; j < K; ++j) wk[j][e] = Elem<T>::ld(w + (size_t)(c0 + e) * K + j);
+    float bv[VN];
+    if (bias) ld16<T>(bias + c0, bv);
+    else
+#pragma unroll
+        for (int e = 0; e < VN; ++e) bv[e] = 0.f;
+    // win[j] = input at token s - (K-1) + j; tokens before 0 come from the state (or are zero)
+    float win[K][VN];
+#pragma unroll
+    for (int j = 0; j < H; ++j) {
+        const int t = s_begin - H + j;
+        if (t >= 0) ld16<T>(xb + (size_t)t * C, win[j]);
+        else if (state_in) ld16<T>(state_in + ((size_t)b * H + (H + t)) * C + c0, win[j]);
+        else
+#pragma unroll
+            for (int e = 0; e < VN; ++e) win[j][e] = 0.f;
+    }
+    // the new state (last K-1 inputs of [state ; x]) is written by the block that owns the last tokens;
+    // entries that stay in the old state are read here, before anything is stored (in-place update)
+    const bool owns_state = state_out != nullptr && s_end == S;
+    float keep[K][VN];
+    if (owns_state && S < H) {
+#pragma unroll
+        for (int j = 0; j < H; ++j) {
+            if (j < H - S) {
+                if (state_in) ld16<T>(state_in + ((size_t)b * H + (j + S)) * C + c0, keep[j]);
+                else
+#pragma unroll
+                    for (int e = 0; e < VN; ++e) keep[j][e] = 0.f;
+            }
+        }
+    }
+    for (int s = s_begin; s < s_end; ++s) {
+        ld16<T>(xb + (size_t)s * C, win[H]);
+        float acc[VN];
+#pragma unroll
+        for (int e = 0; e < VN; ++e) acc[e] = bv[e];
+#pragma unroll
+        for (int j = 0; j < K; ++j)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) acc[e] = fmaf(wk[j][e], win[j][e], acc[e]);
+        if (act_silu)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) acc[e] = silu(acc[e]);
+        st16<T>(yb + (size_t)s * C, acc);
+#pragma unroll
+        for (int j = 0; j < H; ++j)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) win[j][e] = win[j + 1][e];
+    }
+    if (owns_state) {
+#pragma unroll
+        for (int j = 0; j < H; ++j) {
+            const int t = S - H + j;                        // token held by state slot j
+            float tmp[VN];
+            if (t >= 0) {
+                ld16<T>(xb + (size_t)t * C, tmp);
+                st16<T>(state_out + ((size_t)b * H + j) * C + c0, tmp);
+            } else {
+                st16<T>(state_out + ((size_t)b * H + j) * C + c0, keep[j]);
+            }
+        }
+    }
+}
+
+}  // namespace xl
+
+using namespace xl;
+
+static inline bool dtype_ok(int dtype) { return dtype == XLSTM_F32 || dtype == XLSTM_BF16; }
+
+extern "C" int xlstm_rms_norm(const void *x, const void *w, void *y, int64_t rows, int cols, float eps, int dtype,
+                              void *stream) {
+    if (rows < 0 || cols <= 0 || (rows > 0 && (!x || !y))) return XLSTM_ERR_INVALID;
+    if (!dtype_ok(dtype)) return XLSTM_ERR_UNSUPPORTED;
+    if (rows == 0) return XLSTM_OK;
+    if (rows > 0x7fffffffLL) return XLSTM_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == XLSTM_F32 ? rms_norm_launch<float>(x, nullptr, w, nullptr, y, rows, cols, eps, st)
+                              : rms_norm_launch<__nv_bfloat16>(x, nullptr, w, nullptr, y, rows, cols, eps, st);
+}
+
+extern "C" int xlstm_add_rms_norm(const void *x, const void *r, const void *w, void *sum, void *y, int64_t rows,
+                                  int cols, float eps, int dtype, void *stream) {
+    if (rows < 0 || cols <= 0 || (rows > 0 && (!x || !r || !sum || !y))) return XLSTM_ERR_INVALID;
+    if (!dtype_ok(dtype)) return XLSTM_ERR_UNSUPPORTED;
+    if (rows == 0) return XLSTM_OK;
+    if (rows > 0x7fffffffLL) return XLSTM_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == XLSTM_F32 ? rms_norm_launch<float>(x, r, w, sum, y, rows, cols, eps, st)
+                              : rms_norm_launch<__nv_bfloat16>(x, r, w, sum, y, rows, cols, eps, st);
+}
+
+extern "C" int xlstm_mlstm_output_gate(const void *h, const void *ogate, const void *w, void *y, int B, int NH, int S,
+                                       int dv, const int64_t *h_strides, int64_t ogate_ld, float eps, int dtype,
+                                       void *stream) {
+    if (B < 0 || NH <= 0 || S < 0 || dv <= 0) return XLSTM_ERR_INVALID;
+    if (!dtype_ok(dtype)) return XLSTM_ERR_UNSUPPORTED;
+    if (B == 0 || S == 0) return XLSTM_OK;
+    if (!h || !ogate || !y) return XLSTM_ERR_INVALID;
+    const int vn = dtype == XLSTM_F32 ? 4 : 8;
+    int64_t hs[3] = {(int64_t)NH * S * dv, (int64_t)S * dv, (int64_t)dv};   // dense [B,NH,S,dv]
+    if (h_strides) { hs[0] = h_strides[0]; hs[1] = h_strides[1]; hs[2] = h_strides[2]; }
+    const uintptr_t al = reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(ogate) | reinterpret_cast<uintptr_t>(y) |
+                         reinterpret_cast<uintptr_t>(w);
+    const int64_t ldo = ogate_ld > 0 ? ogate_ld : (int64_t)NH * dv;
+    if (ldo < (int64_t)NH * dv) return XLSTM_ERR_INVALID;
+    if (dv % vn || hs[0] % vn || hs[1] % vn || hs[2] % vn || ldo % vn || (al & 15u)) return XLSTM_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == XLSTM_F32 ? output_gate_launch<float>(h, ogate, w, y, B, NH, S, dv, hs, ldo, eps, st)
+                              : output_gate_launch<__nv_bfloat16>(h, ogate, w, y, B, NH, S, dv, hs, ldo, eps, st);
+}
+
+extern "C" int xlstm_swiglu(const void *g, const void *u, void *y, int64_t rows, int cols, int64_t ldg, int64_t ldu,
+                            int dtype, void *stream) {
+    if (rows < 0 || cols <= 0 || ldg < cols || ldu < cols) return XLSTM_ERR_INVALID;
+    if (!dtype_ok(dtype)) return XLSTM_ERR_UNSUPPORTED;
+    if (rows == 0) return XLSTM_OK;
+    if (!g || !u || !y) return XLSTM_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return dtype == XLSTM_F32 ? swiglu_launch<float>(g, u, y, rows, cols, ldg, ldu, st)
+                              : swiglu_launch<__nv_bfloat16>(g, u, y, rows, cols, ldg, ldu, st);
+}
+
+extern "C" int xlstm_causal_conv1d(const void *x, const void *w, const void *bias, const void *state_in, void *state_out,
+                                   void *y, int B, int S, int C, int K, int act_silu, int dtype, void *stream) {
+    if (B < 0 || S < 0 || C <= 0 || K <= 0) return XLSTM_ERR_INVALID;
+    if (!dtype_ok(dtype) || K > CONV_KMAX) return XLSTM_ERR_UNSUPPORTED;
+    if (B == 0 || S == 0) return XLSTM_OK;
+    if (!x || !w || !y) return XLSTM_ERR_INVALID;
+    // the in-place state update is only safe while one token block reads the old state and writes the new one
+    if (state_out && state_out == state_in && S > CONV_T) return XLSTM_ERR_INVALID;
+    const int vn = dtype == XLSTM_F32 ? 4 : 8;
+    const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(bias) |
+                         reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out);
+    if (C % vn || (al & 15u) || B > 65535 || (S + CONV_T - 1) / CONV_T > 65535) return XLSTM_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int cvec = C / vn;
+    const dim3 grid((cvec + 127) / 128, (S + CONV_T - 1) / CONV_T, B);
+#define XL_CONV_CASE(KK)                                                                                              \
+    case KK:                                                                                                          \
+        if (dtype == XLSTM_F32)                                                                                       \
+            causal_conv1d_kernel<float, KK><<<grid, 128, 0, st>>>(                                                    \
+                static_cast<const float *>(x), static_cast<const float *>(w), static_cast<const float *>(bias),      \
+                static_cast<const float *>(state_in), static_cast<float *>(state_out), static_cast<float *>(y), S, C, \
+                act_silu);                                                                                            \
+        else                                                                                                          \
+            causal_conv1d_kernel<__nv_bfloat16, KK><<<grid, 128, 0, st>>>(                                            \
+                static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(w),                         \
+                static_cast<const __nv_bfloat16 *>(bias), static_cast<const __nv_bfloat16 *>(state_in),               \
+                static_cast<__nv_bfloat16 *>(state_out), static_cast<__nv_bfloat16 *>(y), S, C, act_silu);            \
+        break;
+    switch (K) {
+        XL_CONV_CASE(1) XL_CONV_CASE(2) XL_CONV_CASE(3) XL_CONV_CASE(4)
+        XL_CONV_CASE(5) XL_CONV_CASE(6) XL_CONV_CASE(7) XL_CONV_CASE(8)
+        default: return XLSTM_ERR_UNSUPPORTED;
+    }
+#undef XL_CONV_CASE
+    return launch_status();
+}

@@ -10,9 +10,10 @@ safetensors key map) and ``forward`` contract of its reference twin:
 ``mLSTMNeuron``              .../mlstm_neuron.py:21-176 (dispatch rule: mlx_jit/.../mlstm_neuron.py:222-264)
 ``mLSTMBlock``               xlstm_metal/torch_native/blocks/mlstm/mlstm_block.py:69-283
 
-The projection GEMMs, norms and the SwiGLU FFN are torch (cuBLAS) calls; the recurrence, the
-decode step and the gate soft-cap are the hand-written kernels.  q, k, v travel to the
-chunkwise kernel as strided views of the [B,S,NH,d] projection output: no transposed copy.
+The GEMMs are torch (cuBLAS) calls; the recurrence, the decode step, the gate soft-cap, the RMS
+norms, the output epilogue (per-head norm x sigmoid(output gate)) and the SwiGLU gate are the
+hand-written kernels.  q, k, v travel to the chunkwise kernel as strided views of the
+[B,S,NH,d] projection output: no transposed copy.
 """
 from __future__ import annotations
 
@@ -129,9 +130,13 @@ class mLSTMOutputCell(nn.Module):
         self.out_proj = nn.Linear(v_dim, input_size, bias=use_bias)
 
     def forward(self, h: torch.Tensor, x_orig: torch.Tensor) -> torch.Tensor:
-        h_norm = self.norm(h.permute(0, 2, 1, 3))                 # [B,S,NH*DH_v]
-        o_gate = torch.sigmoid(self.ogate_proj(x_orig))           # no soft-cap on the output gate
-        return self.out_proj(h_norm * o_gate)
+        return self.forward_gated(h, self.ogate_proj(x_orig))
+
+    def forward_gated(self, h: torch.Tensor, o_preact: torch.Tensor) -> torch.Tensor:
+        """``o_preact`` = ``ogate_proj(x)`` computed by the caller (a column block of a fused GEMM)."""
+        # norm(h) * sigmoid(ogate) in one pass over h [B,NH,S,dv]; no soft-cap on the output gate
+        gated = ops.mlstm_output_gate(h, o_preact, self.norm.weight, self.norm.eps)
+        return self.out_proj(gated)
 
 
 class mLSTMNeuron(nn.Module):
@@ -169,8 +174,64 @@ class mLSTMNeuron(nn.Module):
     def output_size(self) -> int:
         return self.input_size
 
+    # ---- one GEMM for the six input-side projections ------------------------------------------------
+    def fuse_projections(self) -> None:
+        """Concatenate the q, k, v, igate, fgate and ogate weights into one ``[N, D]`` matrix, so that a
+        block of tokens needs one GEMM instead of six.  The six parameters become views of that
+        matrix (same storage): names, ``state_dict`` and later in-place loads are unchanged.  Moving
+        the module afterwards (``.to``) detaches the views; ``forward`` notices and uses the
+        separate projections until this is called again."""
+        lins = self._fusable()
+        W = torch.cat([l.weight.data for l in lins], dim=0)
+        b = torch.cat([l.bias.data if l.bias is not None else W.new_zeros(l.out_features) for l in lins])
+        off = 0
+        for l in lins:
+            n = l.out_features
+            l.weight.data = W[off:off + n]
+            if l.bias is not None:
+                l.bias.data = b[off:off + n]
+            off += n
+        self._fused = (W, b)
+
+    def _fusable(self):
+        pc = self.projection_cell
+        return [pc.q_proj, pc.k_proj, pc.v_proj, pc.igate_proj, pc.fgate_proj, self.output_cell.ogate_proj]
+
+    def _fused_weights(self):
+        fused = getattr(self, "_fused", None)
+        if fused is None:
+            return None
+        W, b = fused
+        off = 0
+        for l in self._fusable():   # still views of the fused matrix?
+            if l.weight.data_ptr() != W.data_ptr() + off * W.stride(0) * W.element_size() or l.weight.dtype != W.dtype:
+                return None
+            if l.bias is not None and l.bias.data_ptr() != b.data_ptr() + off * b.element_size():
+                return None
+            off += l.out_features
+        return fused
+
+    def _project(self, x: torch.Tensor):
+        fused = self._fused_weights()
+        if fused is None:
+            q, k, v, i_preact, f_preact = self.projection_cell(x)
+            return q, k, v, i_preact, f_preact, None
+        B, S, _ = x.shape
+        NH, dqk, dv = self.num_heads, self.qk_dim_per_head, self.v_dim_per_head
+        y = F.linear(x, fused[0], fused[1])
+        o_k, o_v, o_g, o_o = NH * dqk, 2 * NH * dqk, 2 * NH * dqk + NH * dv, 2 * NH * dqk + NH * dv + 2 * NH
+        q = y[..., :o_k].view(B, S, NH, dqk).permute(0, 2, 1, 3)
+        k = y[..., o_k:o_v].view(B, S, NH, dqk).permute(0, 2, 1, 3)
+        v = y[..., o_v:o_g].view(B, S, NH, dv).permute(0, 2, 1, 3)
+        gates = y[..., o_g:o_o]                                  # [B,S,2*NH]: input gate, forget gate
+        cap = self.projection_cell.gate_soft_cap
+        if cap is not None:
+            gates = ops.softcap(gates, cap)
+        i_preact, f_preact = gates[..., :NH].permute(0, 2, 1), gates[..., NH:].permute(0, 2, 1)
+        return q, k, v, i_preact, f_preact, y[..., o_o:]
+
     def forward(self, x: torch.Tensor, state: Optional[State] = None):
-        q, k, v, i_preact, f_preact = self.projection_cell(x)
+        q, k, v, i_preact, f_preact, o_preact = self._project(x)
         S = q.shape[2]
         use_parallel = self.kernel_mode == "parallel" and self.chunk_size > 0
         chunk_tokens = (S // self.chunk_size) * self.chunk_size if use_parallel else 0
@@ -186,7 +247,9 @@ class mLSTMNeuron(nn.Module):
                                                f_preact[:, :, sl], cur)
             pieces.append(h_seq)
         h = pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=2)
-        return self.output_cell(h, x), cur
+        if o_preact is None:
+            return self.output_cell(h, x), cur
+        return self.output_cell.forward_gated(h, o_preact), cur
 
     def get_config(self) -> dict:
         return {"input_size": self.input_size, "num_heads": self.num_heads, "qk_dim_per_head": self.qk_dim_per_head,
@@ -235,10 +298,36 @@ class mLSTMBlock(nn.Module):
 
     def forward(self, x: torch.Tensor, state: Optional[State] = None):
         mlstm_out, new_state = self.mlstm_cell(self.norm_mlstm(x), state)
-        x = x + mlstm_out
-        xn = self.norm_ffn(x)
-        x = x + self.ffn_proj_down(F.silu(self.ffn_proj_up_gate(xn)) * self.ffn_proj_up(xn))
+        x, xn = ops.add_rms_norm(x, mlstm_out, self.norm_ffn.weight, self.norm_ffn.eps)   # residual + pre-norm
+        fused = self._fused_ffn()
+        if fused is None:
+            gated = ops.swiglu(self.ffn_proj_up_gate(xn), self.ffn_proj_up(xn))
+        else:
+            y = F.linear(xn, fused)
+            gated = ops.swiglu(y[..., :self.ffn_hidden_dim], y[..., self.ffn_hidden_dim:])
+        x = x + self.ffn_proj_down(gated)
         return x, new_state
+
+    def fuse_projections(self) -> None:
+        """One GEMM for the six input-side projections of the mLSTM layer and one for the two up
+        projections of the FFN; the parameters become views of the fused matrices (see
+        ``mLSTMNeuron.fuse_projections``)."""
+        self.mlstm_cell.fuse_projections()
+        if self.ffn_proj_up.bias is None and self.ffn_proj_up_gate.bias is None:
+            W = torch.cat([self.ffn_proj_up_gate.weight.data, self.ffn_proj_up.weight.data], dim=0)
+            self.ffn_proj_up_gate.weight.data = W[:self.ffn_hidden_dim]
+            self.ffn_proj_up.weight.data = W[self.ffn_hidden_dim:]
+            self._fused_ffn_w = W
+
+    def _fused_ffn(self):
+        W = getattr(self, "_fused_ffn_w", None)
+        if W is None:
+            return None
+        row = W.stride(0) * W.element_size()
+        if (self.ffn_proj_up_gate.weight.data_ptr() != W.data_ptr() or self.ffn_proj_up_gate.weight.dtype != W.dtype or
+                self.ffn_proj_up.weight.data_ptr() != W.data_ptr() + self.ffn_hidden_dim * row):
+            return None
+        return W
 
     def get_weight_keys(self) -> Dict[str, str]:
         p = f"backbone.blocks.{self.block_index}"

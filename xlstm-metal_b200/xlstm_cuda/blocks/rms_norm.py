@@ -1,4 +1,5 @@
-"""Normalisation cells around the hot path (torch ops; reductions in fp32).
+"""Normalisation cells around the hot path: RMS norms run the ``rms_norm`` kernel (fp32 math, one
+rounding); like every kernel-backed cell they need CUDA tensors.
 
 ``RMSNormCell``        xlstm_metal/torch_native/blocks/rms_norm/rmsnorm.py:11-43 (math:
                        rms_norm_kernel.metal:20-30, tests/parity/canonical_reference.py:26-33)
@@ -9,6 +10,8 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
+
+from .. import ops
 
 
 class RMSNormCell(nn.Module):
@@ -23,11 +26,7 @@ class RMSNormCell(nn.Module):
             self.register_parameter("weight", None)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        xf = x.to(torch.float32) if self.force_float32 else x
-        y = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + self.eps)
-        if self.weight is not None:
-            y = y * self.weight.to(y.dtype)
-        return y.to(x.dtype)
+        return ops.rms_norm(x, self.weight, self.eps)
 
 
 class MultiHeadRMSNorm(nn.Module):
@@ -45,10 +44,9 @@ class MultiHeadRMSNorm(nn.Module):
         B, S, NH, DH = x.shape
         if NH != self.num_heads or DH != self.head_dim:
             raise ValueError(f"Expected shape [B,S,{self.num_heads},{self.head_dim}], got {x.shape}")
-        rms = torch.sqrt(x.float().pow(2).mean(dim=-1, keepdim=True) + self.eps)
-        y = (x / rms).type_as(x).reshape(B, S, NH * DH)
+        y = ops.rms_norm(x, None, self.eps).reshape(B, S, NH * DH)
         if self.weight is not None:
-            y = y * self.weight
+            y = y * self.weight.to(y.dtype)
         return y
 
 

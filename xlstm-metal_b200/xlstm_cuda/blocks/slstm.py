@@ -58,8 +58,18 @@ class CausalConv1d(nn.Module):
         self.conv = nn.Conv1d(in_channels, out_channels, kernel_size, groups=groups, bias=bias)
         self.padding = kernel_size - 1
 
+    @property
+    def depthwise(self) -> bool:
+        return self.conv.groups == self.conv.in_channels == self.conv.out_channels
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.depthwise:   # [B,C,S] -> channels-last kernel -> [B,C,S]
+            return ops.causal_conv1d(x.permute(0, 2, 1), self.conv.weight, self.conv.bias).permute(0, 2, 1)
         return self.conv(F.pad(x, (self.padding, 0)) if self.padding > 0 else x)
+
+    def forward_tokens(self, x: torch.Tensor, silu: bool = False) -> torch.Tensor:
+        """Depthwise path on ``[B,S,C]`` directly (no transposes), optional fused SiLU."""
+        return ops.causal_conv1d(x, self.conv.weight, self.conv.bias, silu=silu)
 
 
 class sLSTMProjectionCell(nn.Module):
@@ -83,7 +93,7 @@ class sLSTMProjectionCell(nn.Module):
     def forward(self, x: torch.Tensor):
         B, S, _ = x.shape
         if self.conv1d is not None:
-            x_conv = F.silu(self.conv1d(x.permute(0, 2, 1))).permute(0, 2, 1)
+            x_conv = self.conv1d.forward_tokens(x, silu=True)   # causal depthwise conv + SiLU, one kernel
         else:
             x_conv = x
         i_preact = self.soft_cap(self.igate_proj(x_conv))
@@ -163,7 +173,7 @@ class sLSTMBlock(nn.Module):
         out, new_state = self.slstm_cell(self.norm_slstm(x), state)
         x = x + out
         xn = self.norm_ffn(x)
-        x = x + self.ffn_proj_down(F.silu(self.ffn_proj_up_gate(xn)) * self.ffn_proj_up(xn))
+        x = x + self.ffn_proj_down(ops.swiglu(self.ffn_proj_up_gate(xn), self.ffn_proj_up(xn)))
         return x, new_state
 
     def get_weight_keys(self) -> Dict[str, str]:

@@ -49,6 +49,7 @@ class xLSTMRunner:
                                 compute_dtype=self.compute_dtype, state_dtype=self.state_dtype,
                                 norm_reduce_force_float32=self.norm_reduce_force_float32, device=device)
         self.model.eval()
+        self.model.fuse_projections()   # one GEMM for q,k,v,i,f,o and one for the FFN up projections per block
         self.state = None
         self._graph = None          # captured single-token decode step (see _decode_step_graph)
         self.tokenizer = None

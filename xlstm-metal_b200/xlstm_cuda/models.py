@@ -72,6 +72,16 @@ class WiredxLSTM(nn.Module):
         logits = self.lm_head(x) if self.lm_head is not None else x
         return (logits, new_states) if return_last_states else logits
 
+    def fuse_projections(self) -> int:
+        """Merge the per-block projection GEMMs (see ``mLSTMBlock.fuse_projections``); returns the
+        number of blocks fused.  Parameter names and values are unchanged."""
+        n = 0
+        for block in self.blocks:
+            if hasattr(block, "fuse_projections"):
+                block.fuse_projections()
+                n += 1
+        return n
+
     def load_pretrained_weights(self) -> None:
         if self.model_dir is None:
             raise ValueError("model_dir must be provided to load weights")

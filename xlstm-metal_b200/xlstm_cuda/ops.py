@@ -190,3 +190,91 @@ def slstm_recurrent(gx, R, rb, state=None, num_heads: int = 4, cap: Optional[flo
         *(o.data_ptr() for o in outs), B, S, num_heads, dh, float(cap) if cap else 0.0, dt, _stream()),
         "xlstm_slstm_recurrent")
     return hs, tuple(outs)
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
+    """RMSNorm over the last dimension; ``weight`` (or None) is cast to ``x.dtype``."""
+    _need_cuda(x, weight)
+    cols = x.shape[-1]
+    xc = x.contiguous()
+    w = None if weight is None else weight.to(xc.dtype).contiguous()
+    y = torch.empty_like(xc)
+    rows = xc.numel() // cols if cols else 0
+    _lib.check(_lib.load().xlstm_rms_norm(xc.data_ptr(), _ptr(w), y.data_ptr(), rows, cols, float(eps), _dtype_code(xc),
+                                          _stream()), "xlstm_rms_norm")
+    return y
+
+
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6):
+    """``s = x + residual`` and ``RMSNorm(s) * weight`` in one pass; returns ``(s, normed)``."""
+    _need_cuda(x, residual, weight)
+    cols = x.shape[-1]
+    xc, rc = x.contiguous(), residual.to(x.dtype).contiguous()
+    w = None if weight is None else weight.to(xc.dtype).contiguous()
+    s, y = torch.empty_like(xc), torch.empty_like(xc)
+    rows = xc.numel() // cols if cols else 0
+    _lib.check(_lib.load().xlstm_add_rms_norm(xc.data_ptr(), rc.data_ptr(), _ptr(w), s.data_ptr(), y.data_ptr(), rows, cols,
+                                              float(eps), _dtype_code(xc), _stream()), "xlstm_add_rms_norm")
+    return s, y
+
+
+def mlstm_output_gate(h: torch.Tensor, ogate: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-6) -> torch.Tensor:
+    """Per-head RMS norm of ``h [B,NH,S,dv]`` (any strides with a contiguous last dimension) times the
+    flat ``weight [NH*dv]`` times ``sigmoid(ogate [B,S,NH*dv])`` -> ``[B,S,NH*dv]``.  ``ogate`` may be a
+    column block of a wider ``[B,S,N]`` tensor (a fused projection output)."""
+    _need_cuda(h, ogate, weight)
+    B, NH, S, dv = h.shape
+    if h.stride(3) != 1:
+        h = h.contiguous()
+    og = ogate.to(h.dtype)
+    ld = og.stride(1) if og.dim() == 3 else NH * dv
+    if og.dim() != 3 or og.stride(2) != 1 or (B > 1 and og.stride(0) != S * ld) or ld < NH * dv:
+        og = og.contiguous()
+        ld = NH * dv
+    w = None if weight is None else weight.to(h.dtype).contiguous()
+    y = torch.empty(B, S, NH * dv, dtype=h.dtype, device=h.device)
+    strides = (ctypes.c_int64 * 3)(h.stride(0), h.stride(1), h.stride(2))
+    _lib.check(_lib.load().xlstm_mlstm_output_gate(h.data_ptr(), og.data_ptr(), _ptr(w), y.data_ptr(), B, NH, S, dv,
+                                                   strides, ld, float(eps), _dtype_code(h), _stream()),
+               "xlstm_mlstm_output_gate")
+    return y
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` over ``[..., cols]``; the two may be column blocks of one wider tensor
+    (row stride larger than ``cols``), the result is dense."""
+    _need_cuda(gate, up)
+    cols = gate.shape[-1]
+    g2, u2 = gate.reshape(-1, cols), up.to(gate.dtype).reshape(-1, cols)
+    if g2.stride(1) != 1:
+        g2 = g2.contiguous()
+    if u2.stride(1) != 1:
+        u2 = u2.contiguous()
+    rows = g2.shape[0]
+    y = torch.empty(*gate.shape[:-1], cols, dtype=gate.dtype, device=gate.device)
+    ldg = g2.stride(0) if rows > 1 else cols
+    ldu = u2.stride(0) if rows > 1 else cols
+    _lib.check(_lib.load().xlstm_swiglu(g2.data_ptr(), u2.data_ptr(), y.data_ptr(), rows, cols, ldg, ldu,
+                                        _dtype_code(g2), _stream()), "xlstm_swiglu")
+    return y
+
+
+def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, silu: bool = False,
+                  state: Optional[torch.Tensor] = None, return_state: bool = False):
+    """Causal depthwise convolution over tokens of ``x [B,S,C]`` (channels last) with ``weight [C,K]``
+    (or the ``[C,1,K]`` weight of a depthwise ``nn.Conv1d``), optional SiLU.  ``state [B,K-1,C]``
+    holds the inputs before the first token (None = zeros); with ``return_state`` the last K-1
+    inputs come back as the state for the next call."""
+    _need_cuda(x, weight, bias, state)
+    B, S, C = x.shape
+    K = weight.shape[-1]
+    xc = x.contiguous()
+    w = weight.to(xc.dtype).reshape(C, K).contiguous()
+    b = None if bias is None else bias.to(xc.dtype).contiguous()
+    st_in = None if state is None else state.to(xc.dtype).contiguous()
+    st_out = torch.empty(B, K - 1, C, dtype=xc.dtype, device=xc.device) if return_state else None
+    y = torch.empty_like(xc)
+    _lib.check(_lib.load().xlstm_causal_conv1d(xc.data_ptr(), w.data_ptr(), _ptr(b), _ptr(st_in), _ptr(st_out),
+                                               y.data_ptr(), B, S, C, K, int(bool(silu)), _dtype_code(xc), _stream()),
+               "xlstm_causal_conv1d")
+    return (y, st_out) if return_state else y
