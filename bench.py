@@ -358,6 +358,7 @@ def run_ours(args):
         line["slstm"] = run_slstm(torch, dist, device, world, rank)
         if rank == 0:
             line["softcap"] = run_softcap(torch, ops, device)
+            line["glue"] = run_glue(torch, ops, device)
             if not args.no_model:
                 line["model"] = run_model(torch, device, 2048, 256)
     if rank == 0:
@@ -468,6 +469,48 @@ def run_softcap(torch, ops, device):
     gbs = 2 * x.numel() * 4 / (ms * 1e-3) / 1e9
     return {"workload": "softcap [2048,50304] fp32 cap=30", "ms": ms,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_source": which}}
+
+
+def run_glue(torch, ops, device):
+    """The HBM-bound kernels either side of the cells at 7B-shaped sizes (bf16, every tensor > L2):
+    algorithmic bytes = each input read once + each output written once."""
+    hbm, _, which = peaks()
+    bf = torch.bfloat16
+    out = {}
+
+    def leg(name, workload, nbytes, fn):
+        fn()
+        ms = _time_cuda(torch, fn, 5)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"workload": workload, "ms": ms, "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s",
+                                                                  "frac": gbs / hbm, "peak_source": which}}
+
+    rows, d = 65536, 4096
+    x = torch.randn(rows, d, device=device).to(bf)
+    r = torch.randn(rows, d, device=device).to(bf)
+    w = torch.ones(d, device=device, dtype=bf)
+    leg("rms_norm", f"RMSNorm [{rows},{d}] bf16", 2 * rows * d * 2, lambda: ops.rms_norm(x, w, 1e-6))
+    leg("add_rms_norm", f"residual add + RMSNorm [{rows},{d}] bf16", 4 * rows * d * 2, lambda: ops.add_rms_norm(x, r, w, 1e-6))
+    del r
+    B, NH, S, dv = 4, 8, 8192, 512
+    h = torch.randn(B, NH, S, dv, device=device).to(bf)
+    og = torch.randn(B, S, NH * dv, device=device).to(bf)
+    wv = torch.ones(NH * dv, device=device, dtype=bf)
+    leg("mlstm_output_gate", f"per-head RMS norm x sigmoid(ogate), h [{B},{NH},{S},{dv}] bf16", 3 * h.numel() * 2,
+        lambda: ops.mlstm_output_gate(h, og, wv, 1e-6))
+    del h, og
+    rows, f = 16384, 10944
+    gu = torch.randn(rows, 2 * f, device=device).to(bf)
+    leg("swiglu", f"silu(gate)*up, two column blocks of [{rows},{2 * f}] bf16", 3 * rows * f * 2,
+        lambda: ops.swiglu(gu[:, :f], gu[:, f:]))
+    del gu
+    Bc, Sc, C = 32, 4096, 1024
+    xc = torch.randn(Bc, Sc, C, device=device).to(bf)
+    wc = torch.randn(C, 4, device=device).to(bf)
+    bc = torch.zeros(C, device=device, dtype=bf)
+    leg("causal_conv1d", f"depthwise causal conv K=4 + SiLU, x [{Bc},{Sc},{C}] bf16", 2 * xc.numel() * 2,
+        lambda: ops.causal_conv1d(xc, wc, bc, silu=True))
+    return out
 
 
 def run_slstm(torch, dist, device, world, rank):

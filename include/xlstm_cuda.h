@@ -168,6 +168,24 @@ int xlstm_slstm_recurrent(const void *gx, const void *R, const float *rb,
                           int B, int S, int NH, int dh, float cap, int dtype, void *stream);
 
 /*
+ * Gate soft-cap folded into the consumers: the same two functions with the raw gate projections as
+ * input; i and f pass through cap * tanh(x / cap) (in fp32) as they are read when gate_cap > 0.
+ * Removes the separate soft-cap pass and its round trip of mLSTMProjectionCell.forward
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/mlstm_projection_cell.py:97-104); logsigmoid,
+ * the in-chunk cumulative sums and the [B,S,NH] -> [B,NH,S] transpose (strides) were already inside
+ * (mlx_jit/.../mlstm_parallel_kernel_cell.py:211-217).
+ */
+int xlstm_mlstm_step_gatecap(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                             const float *C0, const float *n0, const float *m0,
+                             void *h, float *C1, float *n1, float *m1,
+                             int B, int NH, int dqk, int dv, float eps, float gate_cap, int dtype, void *stream);
+int xlstm_mlstm_chunkwise_fwd_gatecap(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                      const float *C0, const float *n0, const float *m0,
+                                      void *h, float *C1, float *n1, float *m1,
+                                      int B, int NH, int S, int dqk, int dv, int L, float eps, float gate_cap, int dtype,
+                                      const int64_t *strides, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * ---- the callers either side of the cells: norm, output epilogue, FFN gate, causal convolution ----
  * One pass over HBM each, 16-byte accesses, fp32 math, one rounding to `dtype` on the way out.
  */

@@ -365,3 +365,40 @@ def test_errors_are_statuses_not_crashes(ops):
         ops.softcap(torch.zeros(4), 15.0)  # CPU tensor: no fallback
     with pytest.raises(TypeError):
         ops.softcap(torch.zeros(4, device="cuda", dtype=torch.float16), 15.0)
+
+
+# ---- gate soft-cap folded into the kernels -------------------------------------------------
+@pytest.mark.parametrize("dtype,shape", [(torch.float32, (2, 3, 200, 64, 64)), (torch.bfloat16, (2, 2, 300, 256, 256))])
+def test_gate_cap_inside_the_kernels(ops, dtype, shape):
+    """Raw gate projections + gate_cap give what pre-capped gates give: chunkwise (exact path in
+    fp32, tensor-core path + exact tail in bf16) and the decode step."""
+    B, NH, S, dqk, dv = shape
+    rng = np.random.default_rng(S)
+    q, k = (rng.standard_normal((B, NH, S, dqk)).astype(np.float32) for _ in range(2))
+    v = rng.standard_normal((B, NH, S, dv)).astype(np.float32)
+    i_raw = (rng.standard_normal((B, NH, S)) * 12.0).astype(np.float32)       # well into the tanh knee
+    f_raw = (rng.standard_normal((B, NH, S)) * 12.0 + 4.0).astype(np.float32)
+    if dtype == torch.bfloat16:
+        q, k, v, i_raw, f_raw = (xo.bf16_round(a) for a in (q, k, v, i_raw, f_raw))
+    cap = 15.0
+    i_cap, f_cap = xo.softcap(i_raw, cap), xo.softcap(f_raw, cap)
+    h_ref, (C_ref, n_ref, m_ref) = xo.mlstm_recurrent(q, k, v, i_cap, f_cap, None, 1e-6)
+    tol = FP32_TOL if dtype == torch.float32 else BF16_TOL
+    h, (C, n, m) = ops.mlstm_chunkwise(dev(q, dtype), dev(k, dtype), dev(v, dtype), dev(i_raw, dtype), dev(f_raw, dtype),
+                                       None, 64, 1e-6, gate_cap=cap)
+    assert relerr(host(h), h_ref) <= tol and relerr(host(C), C_ref) <= tol and relerr(host(n), n_ref) <= tol
+    assert np.abs(host(m) - m_ref).max() <= (1e-4 if dtype == torch.float32 else 2e-2)
+    # decode steps from that state, raw gates again
+    st, st_ref = (C, n, m), (C_ref, n_ref, m_ref)
+    for t in range(3):
+        qs, ks, vs = q[:, :, t], k[:, :, t], v[:, :, t]
+        hs, st = ops.mlstm_step(dev(qs, dtype), dev(ks, dtype), dev(vs, dtype), dev(i_raw[:, :, t], dtype),
+                                dev(f_raw[:, :, t], dtype), st, 1e-6, gate_cap=cap)
+        hr, st_ref = xo.mlstm_recurrent(qs[:, :, None], ks[:, :, None], vs[:, :, None], i_cap[:, :, t:t + 1],
+                                        f_cap[:, :, t:t + 1], st_ref, 1e-6)
+        assert relerr(host(hs), hr[:, :, 0]) <= tol
+    # cap <= 0 / None: gates are taken as given
+    h0, _ = ops.mlstm_chunkwise(dev(q, dtype), dev(k, dtype), dev(v, dtype), dev(i_cap, dtype), dev(f_cap, dtype), None, 64, 1e-6)
+    h1, _ = ops.mlstm_chunkwise(dev(q, dtype), dev(k, dtype), dev(v, dtype), dev(i_cap, dtype), dev(f_cap, dtype), None, 64, 1e-6,
+                                gate_cap=0.0)
+    assert torch.equal(h0, h1)

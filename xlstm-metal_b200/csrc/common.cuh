@@ -43,6 +43,8 @@ __device__ __forceinline__ void st4(__nv_bfloat16 *p, float4 v) {
 // fp32 rounding on the soft-capped range |x| <= 15 and finite everywhere.
 __device__ __forceinline__ float logsigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+// gate soft-cap folded into the kernels that consume the gates: cap <= 0 leaves x as it is
+__device__ __forceinline__ float gate_softcap(float x, float cap) { return cap > 0.0f ? cap * tanhf(x / cap) : x; }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

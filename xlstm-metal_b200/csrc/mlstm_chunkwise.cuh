@@ -11,6 +11,7 @@ struct ChunkwiseParams {
     float *C1, *n1, *m1;
     int B, NH, S, dqk, dv, L;
     float eps, qscale;
+    float gate_cap;   // > 0: i and f are soft-capped (cap * tanh(x / cap)) as they are read
     // element strides (batch, head, token); innermost dimension contiguous
     int64_t sq[3], sk[3], sv[3], sh[3], sg[3];
     // optional extra destinations of h (same strides and offsets as `h`): buffers of peer GPUs

@@ -25,7 +25,8 @@ static int chunkwise_dispatch(const void *q, const void *k, const void *v, const
                               const float *C0, const float *n0, const float *m0, void *h, float *C1,
                               float *n1, float *m1, int B, int NH, int S, int dqk, int dv, int L,
                               float eps, int dtype, const int64_t *strides, void *workspace,
-                              size_t workspace_bytes, void *stream, void *const *h_peers, int n_peers) {
+                              size_t workspace_bytes, void *stream, void *const *h_peers, int n_peers,
+                              float gate_cap = 0.0f) {
     if (!q || !k || !v || !ig || !fg || !h || !C1 || !n1 || !m1) return XLSTM_ERR_INVALID;
     if (B <= 0 || NH <= 0 || S <= 0 || dqk <= 0 || dv <= 0 || L <= 0) return XLSTM_ERR_INVALID;
     if (C0 && (!n0 || !m0)) return XLSTM_ERR_INVALID;
@@ -40,6 +41,7 @@ static int chunkwise_dispatch(const void *q, const void *k, const void *v, const
     p.h = h; p.C1 = C1; p.n1 = n1; p.m1 = m1;
     p.B = B; p.NH = NH; p.S = S; p.dqk = dqk; p.dv = dv; p.L = L;
     p.eps = eps; p.qscale = 1.0f / sqrtf((float)dqk);
+    p.gate_cap = gate_cap;
     if (strides) {
         for (int d = 0; d < 3; ++d) {
             p.sq[d] = strides[d]; p.sk[d] = strides[3 + d]; p.sv[d] = strides[6 + d];
@@ -87,4 +89,14 @@ extern "C" int xlstm_mlstm_chunkwise_fwd_gather(const void *q, const void *k, co
                                                 int n_peers, void *stream) {
     return chunkwise_dispatch(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, S, dqk, dv, L, eps, dtype, strides,
                               workspace, workspace_bytes, stream, h_peers, n_peers);
+}
+
+extern "C" int xlstm_mlstm_chunkwise_fwd_gatecap(const void *q, const void *k, const void *v, const void *ig,
+                                                 const void *fg, const float *C0, const float *n0, const float *m0,
+                                                 void *h, float *C1, float *n1, float *m1, int B, int NH, int S,
+                                                 int dqk, int dv, int L, float eps, float gate_cap, int dtype,
+                                                 const int64_t *strides, void *workspace, size_t workspace_bytes,
+                                                 void *stream) {
+    return chunkwise_dispatch(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, S, dqk, dv, L, eps, dtype, strides,
+                              workspace, workspace_bytes, stream, nullptr, 0, gate_cap);
 }

@@ -95,8 +95,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_simt_kernel(Chunkw
         // in double: the differences stay exact to fp32 rounding of the result.
         if (tid < LT) {
             const bool valid = tid < Lc;
-            sFl[tid] = valid ? logsigmoid(Elem<T>::ld(fb + (int64_t)(t0 + tid) * p.sg[2])) : 0.f;
-            sI[tid] = valid ? Elem<T>::ld(ib + (int64_t)(t0 + tid) * p.sg[2]) : -INFINITY;
+            sFl[tid] = valid ? logsigmoid(gate_softcap(Elem<T>::ld(fb + (int64_t)(t0 + tid) * p.sg[2]), p.gate_cap)) : 0.f;
+            sI[tid] = valid ? gate_softcap(Elem<T>::ld(ib + (int64_t)(t0 + tid) * p.sg[2]), p.gate_cap) : -INFINITY;
         }
         __syncthreads();
         if (tid < LT) {

@@ -32,7 +32,7 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
                   const T *__restrict__ ig, const T *__restrict__ fg,
                   const float *C0, const float *__restrict__ n0, const float *__restrict__ m0,
                   T *__restrict__ h, float *C1, float *__restrict__ n1, float *__restrict__ m1,
-                  int dqk, int dv, float eps, float qscale) {
+                  int dqk, int dv, float eps, float qscale, float gate_cap) {
     constexpr int CV = DVT / 4;       // 128-bit column vectors per row of the tile
     constexpr int RG = THREADS / CV;  // row groups walking the rows in parallel
     extern __shared__ float smem[];
@@ -62,8 +62,8 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
     }
 
     // stabilised gates (every thread: two exps and a log1p are cheaper than a broadcast)
-    const float it = Elem<T>::ld(ig + bh);
-    const float flog = logsigmoid(Elem<T>::ld(fg + bh));
+    const float it = gate_softcap(Elem<T>::ld(ig + bh), gate_cap);
+    const float flog = logsigmoid(gate_softcap(Elem<T>::ld(fg + bh), gate_cap));
     const float mold = has_state ? m0[bh] : 0.0f;
     const float mnew = fmaxf(flog + mold, it);
     const float fgate = expf(flog + mold - mnew);
@@ -136,7 +136,7 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
 template <typename T>
 static int mlstm_step_launch(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                              const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
-                             float *m1, int BH, int dqk, int dv, float eps, cudaStream_t st) {
+                             float *m1, int BH, int dqk, int dv, float eps, float gate_cap, cudaStream_t st) {
     constexpr int DVT = XL_STEP_DVT, THREADS = XL_STEP_THREADS, UNROLL = XL_STEP_UNROLL;
     dim3 grid(BH, (dv + DVT - 1) / DVT);
     size_t smem = sizeof(float) * (2 * (size_t)dqk + (THREADS / (DVT / 4)) * DVT);
@@ -149,15 +149,16 @@ static int mlstm_step_launch(const void *q, const void *k, const void *v, const 
     kern<<<grid, THREADS, smem, st>>>(static_cast<const T *>(q), static_cast<const T *>(k),
                                       static_cast<const T *>(v), static_cast<const T *>(ig),
                                       static_cast<const T *>(fg), C0, n0, m0, static_cast<T *>(h), C1, n1, m1,
-                                      dqk, dv, eps, 1.0f / sqrtf((float)dqk));
+                                      dqk, dv, eps, 1.0f / sqrtf((float)dqk), gate_cap);
     return launch_status();
 }
 
 }  // namespace xl
 
-extern "C" int xlstm_mlstm_step(const void *q, const void *k, const void *v, const void *ig, const void *fg,
-                                const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
-                                float *m1, int B, int NH, int dqk, int dv, float eps, int dtype, void *stream) {
+static int mlstm_step_checked(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                              const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
+                              float *m1, int B, int NH, int dqk, int dv, float eps, float gate_cap, int dtype,
+                              void *stream) {
     if (!q || !k || !v || !ig || !fg || !h || !C1 || !n1 || !m1) return XLSTM_ERR_INVALID;
     if (B <= 0 || NH <= 0 || dqk <= 0 || dv <= 0) return XLSTM_ERR_INVALID;
     if (C0 && (!n0 || !m0)) return XLSTM_ERR_INVALID;
@@ -167,6 +168,19 @@ extern "C" int xlstm_mlstm_step(const void *q, const void *k, const void *v, con
     if ((int64_t)B * NH > 2147483647LL || (dv + XL_STEP_DVT - 1) / XL_STEP_DVT > 65535) return XLSTM_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == XLSTM_F32)
-        return xl::mlstm_step_launch<float>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, st);
-    return xl::mlstm_step_launch<__nv_bfloat16>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, st);
+        return xl::mlstm_step_launch<float>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, gate_cap, st);
+    return xl::mlstm_step_launch<__nv_bfloat16>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, gate_cap, st);
+}
+
+extern "C" int xlstm_mlstm_step(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
+                                float *m1, int B, int NH, int dqk, int dv, float eps, int dtype, void *stream) {
+    return mlstm_step_checked(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, dqk, dv, eps, 0.0f, dtype, stream);
+}
+
+extern "C" int xlstm_mlstm_step_gatecap(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                        const float *C0, const float *n0, const float *m0, void *h, float *C1,
+                                        float *n1, float *m1, int B, int NH, int dqk, int dv, float eps, float gate_cap,
+                                        int dtype, void *stream) {
+    return mlstm_step_checked(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, dqk, dv, eps, gate_cap, dtype, stream);
 }

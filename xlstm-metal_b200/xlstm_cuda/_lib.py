@@ -28,6 +28,10 @@ _SIGNATURES = {
                                          + [c_float, c_int, ctypes.POINTER(c_int64), c_void_p]),
     "xlstm_slstm_scan": (c_int, [c_void_p] * 4 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 4 + [c_float, c_int, c_void_p]),
     "xlstm_slstm_recurrent": (c_int, [c_void_p] * 3 + [c_void_p] * 4 + [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p]),
+    "xlstm_mlstm_step_gatecap": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 4
+                                 + [c_float, c_float, c_int, c_void_p]),
+    "xlstm_mlstm_chunkwise_fwd_gatecap": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6
+                                          + [c_float, c_float, c_int, ctypes.POINTER(c_int64), c_void_p, c_size_t, c_void_p]),
     "xlstm_rms_norm": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_float, c_int, c_void_p]),
     "xlstm_add_rms_norm": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_float, c_int, c_void_p]),
     "xlstm_mlstm_output_gate": (c_int, [c_void_p] * 4 + [c_int] * 4 + [ctypes.POINTER(c_int64), c_int64, c_float, c_int, c_void_p]),

@@ -92,13 +92,15 @@ class mLSTMRecurrentKernelCell(_KernelCellBase):
         # reference always returns new tensors; the runner switches this on for graph-captured decode)
         self.inplace_state = False
 
-    def forward(self, q, k, v, i_preact, f_preact, state: Optional[State] = None):
+    def forward(self, q, k, v, i_preact, f_preact, state: Optional[State] = None, gate_cap: Optional[float] = None):
+        """``gate_cap`` (not in the reference signature): the gates are raw projections and the kernel
+        applies the soft-cap itself."""
         q, k, v, i_preact, f_preact = self._cast_in(q, k, v, i_preact, f_preact)
         if q.shape[2] == 1:
             h, st = ops.mlstm_step(q[:, :, 0], k[:, :, 0], v[:, :, 0], i_preact[:, :, 0], f_preact[:, :, 0],
-                                   state, self.eps, inplace=self.inplace_state)
+                                   state, self.eps, inplace=self.inplace_state, gate_cap=gate_cap)
             return h.unsqueeze(2), self._cast_state(st)
-        h, st = ops.mlstm_chunkwise(q, k, v, i_preact, f_preact, state, 64, self.eps)
+        h, st = ops.mlstm_chunkwise(q, k, v, i_preact, f_preact, state, 64, self.eps, gate_cap=gate_cap)
         return h, self._cast_state(st)
 
 
@@ -111,9 +113,9 @@ class mLSTMParallelKernelCell(_KernelCellBase):
         super().__init__(num_heads, qk_dim_per_head, v_dim_per_head, eps, compute_dtype, state_dtype)
         self.chunk_size = chunk_size
 
-    def forward(self, q, k, v, i_preact, f_preact, state: Optional[State] = None):
+    def forward(self, q, k, v, i_preact, f_preact, state: Optional[State] = None, gate_cap: Optional[float] = None):
         q, k, v, i_preact, f_preact = self._cast_in(q, k, v, i_preact, f_preact)
-        h, st = ops.mlstm_chunkwise(q, k, v, i_preact, f_preact, state, self.chunk_size, self.eps)
+        h, st = ops.mlstm_chunkwise(q, k, v, i_preact, f_preact, state, self.chunk_size, self.eps, gate_cap=gate_cap)
         return h, self._cast_state(st)
 
 
@@ -223,15 +225,15 @@ class mLSTMNeuron(nn.Module):
         q = y[..., :o_k].view(B, S, NH, dqk).permute(0, 2, 1, 3)
         k = y[..., o_k:o_v].view(B, S, NH, dqk).permute(0, 2, 1, 3)
         v = y[..., o_v:o_g].view(B, S, NH, dv).permute(0, 2, 1, 3)
-        gates = y[..., o_g:o_o]                                  # [B,S,2*NH]: input gate, forget gate
-        cap = self.projection_cell.gate_soft_cap
-        if cap is not None:
-            gates = ops.softcap(gates, cap)
-        i_preact, f_preact = gates[..., :NH].permute(0, 2, 1), gates[..., NH:].permute(0, 2, 1)
+        # raw gate projections (strided views): the soft-cap is applied inside the kernels
+        i_preact = y[..., o_g:o_g + NH].permute(0, 2, 1)
+        f_preact = y[..., o_g + NH:o_o].permute(0, 2, 1)
         return q, k, v, i_preact, f_preact, y[..., o_o:]
 
     def forward(self, x: torch.Tensor, state: Optional[State] = None):
         q, k, v, i_preact, f_preact, o_preact = self._project(x)
+        # fused projections hand over raw gates; the separate projection cell has already capped them
+        cap = self.projection_cell.gate_soft_cap if o_preact is not None else None
         S = q.shape[2]
         use_parallel = self.kernel_mode == "parallel" and self.chunk_size > 0
         chunk_tokens = (S // self.chunk_size) * self.chunk_size if use_parallel else 0
@@ -239,12 +241,12 @@ class mLSTMNeuron(nn.Module):
         if chunk_tokens > 0:
             sl = slice(0, chunk_tokens)
             h_par, cur = self.parallel_kernel(q[:, :, sl], k[:, :, sl], v[:, :, sl], i_preact[:, :, sl],
-                                              f_preact[:, :, sl], cur)
+                                              f_preact[:, :, sl], cur, gate_cap=cap)
             pieces.append(h_par)
         if S - chunk_tokens > 0:  # the S mod L tail and every decode token go through the recurrent cell
             sl = slice(chunk_tokens, S)
             h_seq, cur = self.recurrent_kernel(q[:, :, sl], k[:, :, sl], v[:, :, sl], i_preact[:, :, sl],
-                                               f_preact[:, :, sl], cur)
+                                               f_preact[:, :, sl], cur, gate_cap=cap)
             pieces.append(h_seq)
         h = pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=2)
         if o_preact is None:

@@ -52,11 +52,13 @@ def softcap(x: torch.Tensor, cap: Optional[float], out: Optional[torch.Tensor] =
     return y.view(x.shape)
 
 
-def mlstm_step(q, k, v, i, f, state=None, eps: float = 1e-6, inplace: bool = False):
+def mlstm_step(q, k, v, i, f, state=None, eps: float = 1e-6, inplace: bool = False,
+               gate_cap: Optional[float] = None):
     """One decode step.  q,k: [B,NH,dqk]; v: [B,NH,dv]; i,f: [B,NH]; state (C,n,m) fp32 or None.
 
     Returns ``h [B,NH,dv]`` and the new state.  ``inplace=True`` overwrites the
     caller's ``C`` (the 2 x dqk x dv x 4 byte stream then hits one buffer).
+    ``gate_cap`` > 0: ``i`` and ``f`` are the raw gate projections and are soft-capped inside the kernel.
     """
     _need_cuda(q, k, v, i, f)
     B, NH, dqk = q.shape
@@ -74,6 +76,12 @@ def mlstm_step(q, k, v, i, f, state=None, eps: float = 1e-6, inplace: bool = Fal
     C1 = C0 if (inplace and C0 is not None) else torch.empty(B, NH, dqk, dv, dtype=torch.float32, device=dev)
     n1 = torch.empty(B, NH, dqk, dtype=torch.float32, device=dev)
     m1 = torch.empty(B, NH, dtype=torch.float32, device=dev)
+    if gate_cap is not None and gate_cap > 0:
+        _lib.check(_lib.load().xlstm_mlstm_step_gatecap(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
+            h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, dqk, dv, float(eps), float(gate_cap), dt,
+            _stream()), "xlstm_mlstm_step_gatecap")
+        return h, (C1, n1, m1)
     _lib.check(_lib.load().xlstm_mlstm_step(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
         h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, dqk, dv, float(eps), dt, _stream()),
@@ -92,14 +100,17 @@ def chunkwise_workspace_bytes(B, NH, S, dqk, dv, L, dtype: torch.dtype) -> int:
 
 def mlstm_chunkwise(q, k, v, i, f, state=None, chunk_size: int = 64, eps: float = 1e-6,
                     workspace: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None,
-                    h_peer_ptrs=None):
+                    h_peer_ptrs=None, gate_cap: Optional[float] = None):
     """Chunkwise forward.  q,k: [B,NH,S,dqk]; v: [B,NH,S,dv]; i,f: [B,NH,S] (any strides with a
     contiguous last dimension, e.g. the permuted [B,S,NH,d] projection output).
 
     ``h_out`` (optional) is a ``[B,NH,S,dv]`` view to write h into (e.g. a head slice of a
     ``[B,S,NH_total,dv]`` buffer); ``h_peer_ptrs`` (optional) are raw device pointers to the same
-    slot in peer GPUs' buffers: the kernel stores every h tile there too (fused all-gather)."""
+    slot in peer GPUs' buffers: the kernel stores every h tile there too (fused all-gather).
+    ``gate_cap`` > 0: ``i`` and ``f`` are the raw gate projections, soft-capped inside the kernels."""
     _need_cuda(q, k, v, i, f)
+    if gate_cap is not None and gate_cap > 0 and h_peer_ptrs:
+        i, f, gate_cap = softcap(i, gate_cap), softcap(f, gate_cap), None   # the gather entry takes capped gates
     B, NH, S, dqk = q.shape
     dv = v.shape[-1]
     dt = _dtype_code(q)
@@ -135,6 +146,12 @@ def mlstm_chunkwise(q, k, v, i, f, state=None, chunk_size: int = 64, eps: float 
             q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
             h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, S, dqk, dv, int(chunk_size), float(eps),
             dt, sarr, _ptr(workspace), wbytes, peers, len(h_peer_ptrs), _stream()), "xlstm_mlstm_chunkwise_fwd_gather")
+        return h, (C1, n1, m1)
+    if gate_cap is not None and gate_cap > 0:
+        _lib.check(_lib.load().xlstm_mlstm_chunkwise_fwd_gatecap(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
+            h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, S, dqk, dv, int(chunk_size), float(eps),
+            float(gate_cap), dt, sarr, _ptr(workspace), wbytes, _stream()), "xlstm_mlstm_chunkwise_fwd_gatecap")
         return h, (C1, n1, m1)
     _lib.check(_lib.load().xlstm_mlstm_chunkwise_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
