@@ -376,8 +376,8 @@ def test_gate_cap_inside_the_kernels(ops, dtype, shape):
     rng = np.random.default_rng(S)
     q, k = (rng.standard_normal((B, NH, S, dqk)).astype(np.float32) for _ in range(2))
     v = rng.standard_normal((B, NH, S, dv)).astype(np.float32)
-    i_raw = (rng.standard_normal((B, NH, S)) * 12.0).astype(np.float32)       # well into the tanh knee
-    f_raw = (rng.standard_normal((B, NH, S)) * 12.0 + 4.0).astype(np.float32)
+    i_raw = (rng.standard_normal((B, NH, S)) * 6.0).astype(np.float32)        # well into the tanh knee
+    f_raw = (rng.standard_normal((B, NH, S)) * 6.0 + 8.0).astype(np.float32)
     if dtype == torch.bfloat16:
         q, k, v, i_raw, f_raw = (xo.bf16_round(a) for a in (q, k, v, i_raw, f_raw))
     cap = 15.0
