@@ -620,7 +620,15 @@ def main():
     ap.add_argument("--prefill-reps", type=int, default=3)
     ap.add_argument("--no-extras", action="store_true", help="skip the soft-cap, sLSTM and full-model sub-benchmarks")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-shaped full-model run")
+    ap.add_argument("--glue-only", action="store_true",
+                    help="time only the HBM-bound kernels either side of the cells (a small command to profile)")
     args = ap.parse_args()
+    if args.glue_only:
+        import torch
+        sys.path.insert(0, str(ROOT / "xlstm-metal_b200"))
+        from xlstm_cuda import ops
+        print(json.dumps({"glue": run_glue(torch, ops, torch.device("cuda:0"))}))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -36,7 +36,31 @@ template <> __device__ __forceinline__ void st16<__nv_bfloat16>(__nv_bfloat16 *p
     *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+// 16 raw bytes already in registers -> VN floats
+template <typename T> __device__ __forceinline__ void unpack16(const uint4 &u, float *f);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4 &u, float *f) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4 &u, float *f) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// sigmoid / SiLU: exact division and expf for fp32 outputs; for bf16 outputs (8 elements per 16 bytes,
+// where these kernels would otherwise be bound by instruction issue, not by HBM) the approximate
+// exp / reciprocal, whose ~2 ulp fp32 error disappears in the bf16 rounding
+template <typename T> __device__ __forceinline__ float sigmoid_t(float x) {
+    if (sizeof(T) == 2) return __frcp_rn(1.0f + __expf(-x));
+    return 1.0f / (1.0f + expf(-x));
+}
+template <typename T> __device__ __forceinline__ float silu_t(float x) {
+    if (sizeof(T) == 2) return x * __frcp_rn(1.0f + __expf(-x));
+    return x / (1.0f + expf(-x));
+}
 
 // ---------------------------------------------------------------------------
 // RMSNorm: one CTA per row, the row cached in registers (NV 16-byte vectors per thread)
@@ -48,12 +72,14 @@ constexpr int RN_THREADS = 128;
 template <typename T, int NV>
 __global__ void __launch_bounds__(RN_THREADS) rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ r,
                                                               const T *__restrict__ w, T *__restrict__ sum,
-                                                              T *__restrict__ y, int cols, float eps) {
+                                                              T *__restrict__ y, int64_t rows, int cols, float eps) {
     constexpr int VN = Vec16<T>::N;
-    __shared__ float s_part[RN_THREADS / 32];
+    __shared__ float s_part[2][RN_THREADS / 32];
     const int nvec = cols / VN;
-    const T *xr = x + (size_t)blockIdx.x * cols;
-    T *yr = y + (size_t)blockIdx.x * cols;
+    int par = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+    const T *xr = x + (size_t)row * cols;
+    T *yr = y + (size_t)row * cols;
     float v[NV][VN];
     float ss = 0.f;
 #pragma unroll
@@ -63,10 +89,10 @@ __global__ void __launch_bounds__(RN_THREADS) rms_norm_kernel(const T *__restric
             ld16<T>(xr + (size_t)iv * VN, v[i]);
             if (r) {
                 float rv[VN];
-                ld16<T>(r + (size_t)blockIdx.x * cols + (size_t)iv * VN, rv);
+                ld16<T>(r + (size_t)row * cols + (size_t)iv * VN, rv);
 #pragma unroll
                 for (int e = 0; e < VN; ++e) v[i][e] += rv[e];
-                st16<T>(sum + (size_t)blockIdx.x * cols + (size_t)iv * VN, v[i]);
+                st16<T>(sum + (size_t)row * cols + (size_t)iv * VN, v[i]);
                 if (sizeof(T) == 2) {
 #pragma unroll
                     for (int e = 0; e < VN; ++e) v[i][e] = __bfloat162float(__float2bfloat16_rn(v[i][e]));
@@ -77,11 +103,11 @@ __global__ void __launch_bounds__(RN_THREADS) rms_norm_kernel(const T *__restric
         }
     }
     ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    if ((threadIdx.x & 31) == 0) s_part[par][threadIdx.x >> 5] = ss;   // two buffers: one barrier per row
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < RN_THREADS / 32; ++i) tot += s_part[i];
+    for (int i = 0; i < RN_THREADS / 32; ++i) tot += s_part[par][i];
     const float inv = rsqrtf(tot / (float)cols + eps);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -93,6 +119,7 @@ __global__ void __launch_bounds__(RN_THREADS) rms_norm_kernel(const T *__restric
             for (int e = 0; e < VN; ++e) v[i][e] = v[i][e] * inv * (w ? wv[e] : 1.0f);
             st16<T>(yr + (size_t)iv * VN, v[i]);
         }
+    }
     }
 }
 
@@ -134,10 +161,10 @@ static int rms_norm_launch(const void *x, const void *r, const void *w, void *su
                          cols % VN == 0;
     const int nvec = cols / VN;
     const dim3 grid((unsigned)rows);
-    if (aligned && nvec <= RN_THREADS * 1) rms_norm_kernel<T, 1><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
-    else if (aligned && nvec <= RN_THREADS * 2) rms_norm_kernel<T, 2><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
-    else if (aligned && nvec <= RN_THREADS * 4) rms_norm_kernel<T, 4><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
-    else if (aligned && nvec <= RN_THREADS * 8) rms_norm_kernel<T, 8><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
+    if (aligned && nvec <= RN_THREADS * 1) rms_norm_kernel<T, 1><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
+    else if (aligned && nvec <= RN_THREADS * 2) rms_norm_kernel<T, 2><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
+    else if (aligned && nvec <= RN_THREADS * 4) rms_norm_kernel<T, 4><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
+    else if (aligned && nvec <= RN_THREADS * 8) rms_norm_kernel<T, 8><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
     else rms_norm_generic_kernel<T><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, cols, eps);
     return launch_status();
 }
@@ -153,40 +180,45 @@ __global__ void __launch_bounds__(OG_WARPS * 32) mlstm_output_gate_kernel(
     int S, int dv, int64_t hsb, int64_t hsh, int64_t hss, int64_t ldo, float eps) {
     constexpr int VN = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * OG_WARPS + (threadIdx.x >> 5);   // (b * S + s) * NH + head
-    if (row >= rows) return;
+    // row = (b * S + s) * NH + head; the warps of the grid walk the rows
+    for (int64_t row = (int64_t)blockIdx.x * OG_WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * OG_WARPS) {
     const int head = (int)(row % NH);
     const int64_t bs = row / NH;
     const int64_t b = bs / S, s = bs % S;
     const T *hr = h + b * hsb + head * hsh + s * hss;
     const int nvec = dv / VN;
-    float v[NV][VN];
-    float ss = 0.f;
+    const T *ogr = og + bs * ldo + (size_t)head * dv;
+    const T *wr = w ? w + (size_t)head * dv : nullptr;
+    T *yr = y + row * dv;
+    // all loads of the row (h and the gate pre-activations) are issued before the reduction
+    float v[NV][VN], o[NV][VN];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int iv = lane + i * 32;
         if (iv < nvec) {
             ld16<T>(hr + (size_t)iv * VN, v[i]);
-#pragma unroll
-            for (int e = 0; e < VN; ++e) ss += v[i][e] * v[i][e];
+            ld16<T>(ogr + (size_t)iv * VN, o[i]);
         }
     }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (lane + i * 32 < nvec)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) ss += v[i][e] * v[i][e];
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
-    const T *ogr = og + bs * ldo + (size_t)head * dv;
-    const T *wr = w ? w + (size_t)head * dv : nullptr;
-    T *yr = y + row * dv;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int iv = lane + i * 32;
         if (iv < nvec) {
-            float o[VN], wv[VN];
-            ld16<T>(ogr + (size_t)iv * VN, o);
+            float wv[VN];
             if (wr) ld16<T>(wr + (size_t)iv * VN, wv);
 #pragma unroll
-            for (int e = 0; e < VN; ++e) v[i][e] = v[i][e] * inv * (wr ? wv[e] : 1.0f) * sigmoidf(o[e]);
+            for (int e = 0; e < VN; ++e) v[i][e] = v[i][e] * inv * (wr ? wv[e] : 1.0f) * sigmoid_t<T>(o[i][e]);
             st16<T>(yr + (size_t)iv * VN, v[i]);
         }
+    }
     }
 }
 
@@ -196,7 +228,8 @@ static int output_gate_launch(const void *h, const void *og, const void *w, void
     constexpr int VN = Vec16<T>::N;
     const int nvec = dv / VN;
     const int64_t rows = (int64_t)B * S * NH;
-    const unsigned grid = (unsigned)((rows + OG_WARPS - 1) / OG_WARPS);
+    const int64_t want = (rows + OG_WARPS - 1) / OG_WARPS;
+    const unsigned grid = (unsigned)(want < 148 * 8 ? want : 148 * 8);
     const T *hp = static_cast<const T *>(h), *op = static_cast<const T *>(og), *wp = static_cast<const T *>(w);
     T *yp = static_cast<T *>(y);
     if (nvec <= 32) mlstm_output_gate_kernel<T, 1><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
@@ -210,22 +243,34 @@ static int output_gate_launch(const void *h, const void *og, const void *w, void
 // ---------------------------------------------------------------------------
 // SwiGLU gate: y[r, c] = silu(g[r, c]) * u[r, c]; g and u may be column blocks of one GEMM output
 // ---------------------------------------------------------------------------
+// One CTA per row at a time (rows by grid stride); the threads walk the row's 16-byte vectors, two per
+// thread per trip so that four loads are in flight.
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const T *__restrict__ g, const T *__restrict__ u, T *__restrict__ y,
                                                      int64_t rows, int cols, int64_t ldg, int64_t ldu) {
     constexpr int VN = Vec16<T>::N;
     const int nvec = cols / VN;
-    const int64_t total = rows * nvec;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t r = i / nvec;
-        const int c = (int)(i % nvec) * VN;
-        float a[VN], b[VN];
-        ld16<T>(g + r * ldg + c, a);
-        ld16<T>(u + r * ldu + c, b);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T *gr = g + r * ldg, *ur = u + r * ldu;
+        T *yr = y + r * cols;
+        for (int v = threadIdx.x; v < nvec; v += 512) {
+            const int v2 = v + 256;
+            float a0[VN], b0[VN], a1[VN], b1[VN];
+            ld16<T>(gr + (size_t)v * VN, a0);
+            ld16<T>(ur + (size_t)v * VN, b0);
+            if (v2 < nvec) {
+                ld16<T>(gr + (size_t)v2 * VN, a1);
+                ld16<T>(ur + (size_t)v2 * VN, b1);
+            }
 #pragma unroll
-        for (int e = 0; e < VN; ++e) a[e] = silu(a[e]) * b[e];
-        st16<T>(y + r * cols + c, a);
+            for (int e = 0; e < VN; ++e) a0[e] = silu_t<T>(a0[e]) * b0[e];
+            st16<T>(yr + (size_t)v * VN, a0);
+            if (v2 < nvec) {
+#pragma unroll
+                for (int e = 0; e < VN; ++e) a1[e] = silu_t<T>(a1[e]) * b1[e];
+                st16<T>(yr + (size_t)v2 * VN, a1);
+            }
+        }
     }
 }
 
@@ -237,7 +282,7 @@ __global__ void swiglu_scalar_kernel(const T *__restrict__ g, const T *__restric
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t r = i / cols;
         const int c = (int)(i % cols);
-        Elem<T>::st(y + i, silu(Elem<T>::ld(g + r * ldg + c)) * Elem<T>::ld(u + r * ldu + c));
+        Elem<T>::st(y + i, silu_t<T>(Elem<T>::ld(g + r * ldg + c)) * Elem<T>::ld(u + r * ldu + c));
     }
 }
 
@@ -247,12 +292,15 @@ static int swiglu_launch(const void *g, const void *u, void *y, int64_t rows, in
     constexpr int VN = Vec16<T>::N;
     const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0 &&
                          cols % VN == 0 && ldg % VN == 0 && ldu % VN == 0;
-    const int64_t work = aligned ? rows * (cols / VN) : rows * cols;
-    int64_t want = (work + 255) / 256;
-    const int grid = (int)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));
     const T *gp = static_cast<const T *>(g), *up = static_cast<const T *>(u);
-    if (aligned) swiglu_kernel<T><<<grid, 256, 0, st>>>(gp, up, static_cast<T *>(y), rows, cols, ldg, ldu);
-    else swiglu_scalar_kernel<T><<<grid, 256, 0, st>>>(gp, up, static_cast<T *>(y), rows, cols, ldg, ldu);
+    if (aligned) {
+        const unsigned grid = (unsigned)(rows < 148 * 8 ? rows : 148 * 8);   // 8 resident CTAs per SM
+        swiglu_kernel<T><<<grid, 256, 0, st>>>(gp, up, static_cast<T *>(y), rows, cols, ldg, ldu);
+    } else {
+        int64_t want = (rows * cols + 255) / 256;
+        const int grid = (int)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));
+        swiglu_scalar_kernel<T><<<grid, 256, 0, st>>>(gp, up, static_cast<T *>(y), rows, cols, ldg, ldu);
+    }
     return launch_status();
 }
 
@@ -261,7 +309,8 @@ static int swiglu_launch(const void *g, const void *u, void *y, int64_t rows, in
 // CONV_T consecutive tokens with the last K-1 inputs in registers, so every input is read once
 // (plus a K-1 halo per token block); a warp covers 32*VN adjacent channels of one token.
 // ---------------------------------------------------------------------------
-constexpr int CONV_T = 16;
+constexpr int CONV_T = 64;          // tokens per thread block: amortises the tap / halo loads
+constexpr int CONV_ALIAS_MAX = 16;  // longest call whose new state may overwrite the old one in place
 constexpr int CONV_KMAX = 8;
 
 template <typename T, int K>
@@ -315,23 +364,33 @@ __global__ void __launch_bounds__(128) causal_conv1d_kernel(const T *__restrict_
             }
         }
     }
-    for (int s = s_begin; s < s_end; ++s) {
-        ld16<T>(xb + (size_t)s * C, win[H]);
-        float acc[VN];
+    // the block's inputs are fetched in batches of 8 tokens, all loads of a batch in flight together
+    for (int s0 = s_begin; s0 < s_end; s0 += 8) {
+        uint4 raw[8];
 #pragma unroll
-        for (int e = 0; e < VN; ++e) acc[e] = bv[e];
+        for (int k = 0; k < 8; ++k)
+            if (s0 + k < s_end) raw[k] = *reinterpret_cast<const uint4 *>(xb + (size_t)(s0 + k) * C);
 #pragma unroll
-        for (int j = 0; j < K; ++j)
+        for (int k = 0; k < 8; ++k) {
+            if (s0 + k < s_end) {
+                unpack16<T>(raw[k], win[H]);
+                float acc[VN];
 #pragma unroll
-            for (int e = 0; e < VN; ++e) acc[e] = fmaf(wk[j][e], win[j][e], acc[e]);
-        if (act_silu)
+                for (int e = 0; e < VN; ++e) acc[e] = bv[e];
 #pragma unroll
-            for (int e = 0; e < VN; ++e) acc[e] = silu(acc[e]);
-        st16<T>(yb + (size_t)s * C, acc);
+                for (int j = 0; j < K; ++j)
 #pragma unroll
-        for (int j = 0; j < H; ++j)
+                    for (int e = 0; e < VN; ++e) acc[e] = fmaf(wk[j][e], win[j][e], acc[e]);
+                if (act_silu)
 #pragma unroll
-            for (int e = 0; e < VN; ++e) win[j][e] = win[j + 1][e];
+                    for (int e = 0; e < VN; ++e) acc[e] = silu_t<T>(acc[e]);
+                st16<T>(yb + (size_t)(s0 + k) * C, acc);
+#pragma unroll
+                for (int j = 0; j < H; ++j)
+#pragma unroll
+                    for (int e = 0; e < VN; ++e) win[j][e] = win[j + 1][e];
+            }
+        }
     }
     if (owns_state) {
 #pragma unroll
@@ -414,7 +473,7 @@ extern "C" int xlstm_causal_conv1d(const void *x, const void *w, const void *bia
     if (B == 0 || S == 0) return XLSTM_OK;
     if (!x || !w || !y) return XLSTM_ERR_INVALID;
     // the in-place state update is only safe while one token block reads the old state and writes the new one
-    if (state_out && state_out == state_in && S > CONV_T) return XLSTM_ERR_INVALID;
+    if (state_out && state_out == state_in && S > CONV_ALIAS_MAX) return XLSTM_ERR_INVALID;
     const int vn = dtype == XLSTM_F32 ? 4 : 8;
     const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(bias) |
                          reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out);
