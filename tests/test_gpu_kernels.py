@@ -352,6 +352,29 @@ def test_slstm_recurrent_oracle(ops, B, S, NH, dh, dtype):
         assert relerr(host(got), want) < (tol if dtype == torch.bfloat16 else FP32_TOL)
 
 
+@pytest.mark.parametrize("B,S,NH", [(1, 5, 1), (33, 70, 2), (32, 600, 4)])
+def test_slstm_recurrent_tensor_core_path(ops, B, S, NH):
+    """bf16 with head dimension 256 runs the tcgen05 kernel (R resident in tensor memory, h fed back as
+    bf16): ragged batch groups, a carried state, and a long sequence for drift."""
+    dh, D = 256, NH * 256
+    rng = np.random.default_rng(B * 1000 + S)
+    gx = rng.standard_normal((B, S, 4, D)).astype(np.float32)
+    gx[:, :, 1] += np.linspace(3, 6, D, dtype=np.float32)
+    gx = xo.bf16_round(gx)
+    R = xo.bf16_round((rng.standard_normal((4, NH, dh, dh)) * 0.02).astype(np.float32))
+    rb = (rng.standard_normal((4, D)) * 0.05).astype(np.float32)
+    bf = torch.bfloat16
+    S1 = S // 2
+    hs_ref, st_ref = xo.slstm_recurrent(gx, R, rb, None, NH, 15.0)
+    hs1, st1 = ops.slstm_recurrent(dev(gx[:, :S1], bf), dev(R, bf), dev(rb), None, NH, 15.0)
+    hs2, st2 = ops.slstm_recurrent(dev(gx[:, S1:], bf), dev(R, bf), dev(rb), st1, NH, 15.0)
+    hs = torch.cat([hs1, hs2], 1)
+    assert torch.isfinite(hs.float()).all()
+    assert relerr(host(hs), hs_ref) < BF16_TOL
+    for got, want in zip(st2, st_ref):
+        assert relerr(host(got), want) < BF16_TOL
+
+
 # ---- error behaviour of the C ABI --------------------------------------------------
 def test_errors_are_statuses_not_crashes(ops):
     from xlstm_cuda import _lib
