@@ -284,7 +284,7 @@ static int slstm_recurrent_launch(const void *gx, const void *R, const float *rb
 
 namespace xl {
 // tensor-core version (slstm_tc.cu): bf16, head dimension 256
-bool slstm_recurrent_tc_supported(int dtype, int dh, const void *R, const void *gx);
+bool slstm_recurrent_tc_supported(int dtype, int dh, const void *R, const void *gx, const void *hs);
 int slstm_recurrent_tc(const void *gx, const void *R, const float *rb, const float *c0, const float *n0, const float *h0,
                        const float *m0, void *hs, float *c1, float *n1, float *h1, float *m1, int B, int S, int NH,
                        float cap, cudaStream_t st);
@@ -322,7 +322,7 @@ extern "C" int xlstm_slstm_recurrent(const void *gx, const void *R, const float 
     if (dtype != XLSTM_F32 && dtype != XLSTM_BF16) return XLSTM_ERR_UNSUPPORTED;
     if (NH > 65535 || (B + xl::REC_BG - 1) / xl::REC_BG > 65535) return XLSTM_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (xl::slstm_recurrent_tc_supported(dtype, dh, R, gx))
+    if (xl::slstm_recurrent_tc_supported(dtype, dh, R, gx, hs))
         return xl::slstm_recurrent_tc(gx, R, rb, c0, n0, h0, m0, hs, c1, n1, h1, m1, B, S, NH, cap, st);
     if (dtype == XLSTM_F32)
         return xl::slstm_recurrent_launch<float>(gx, R, rb, c0, n0, h0, m0, hs, c1, n1, h1, m1, B, S, NH, dh, cap, st);
