@@ -234,6 +234,23 @@ int xlstm_swiglu(const void *g, const void *u, void *y, int64_t rows, int cols, 
                  void *stream);
 
 /*
+ * Linear layer for up to 4 token rows (single-token decode), bf16, as ONE weight-streaming pass with the
+ * neighbouring ops folded in:
+ *   xh[m] = norm_w ? RMSNorm(x[m]; norm_eps) * norm_w : x[m]          (norm_w: [K] or NULL)
+ *   epilogue 0:  y[m,n] = W[n,:] . xh[m] + bias[n]
+ *   epilogue 1:  y[m,n] = residual[m,n] + (W[n,:] . xh[m] + bias[n])   (the block's residual stream)
+ *   epilogue 2:  y[m,n] = silu(W[n,:] . xh[m] + bias[n]) * (W[N+n,:] . xh[m] + bias[N+n])   (W: [2N,K], gate rows first)
+ * W: [N,K] (or [2N,K]) row-major, the layout of nn.Linear.weight; x: [M,K]; y: [M,N]; bias: [N] / [2N] or NULL.
+ * Intermediate results are rounded to bf16 where the separate kernels would round them.
+ * Replaces, for one token, the nn.Linear calls of mLSTMProjectionCell.forward / mLSTMOutputCell.forward
+ * (xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/mlstm_projection_cell.py:85-106,
+ * mlstm_output_cell.py:84-99) and of the FFN (mlstm_block.py:192-206) together with the RMSNorm before
+ * them (rmsnorm.py:30-40), the residual adds and the SwiGLU gate around them.
+ */
+int xlstm_linear_token(const void *W, const void *x, const void *bias, const void *norm_w, float norm_eps,
+                       const void *residual, void *y, int M, int N, int K, int epilogue, int dtype, void *stream);
+
+/*
  * Causal depthwise convolution over tokens, channels last, optional SiLU:
  *   y[b,s,c] = act(bias[c] + sum_{j<K} w[c,j] * x[b, s-(K-1)+j, c]),   K <= 8.
  * x, y: [B,S,C]; w: [C,K] (the [C,1,K] weight of a depthwise nn.Conv1d); bias: [C] or NULL.

@@ -107,6 +107,17 @@ def mlstm_output_gate(h, og, w, eps: float):
     return y
 
 
+def linear(x, W, bias=None):
+    """x: [..., K]; W: [N, K]; bias: [N] -> [..., N]."""
+    x, W = _c(x), _c(W)
+    bias = None if bias is None else _c(bias)
+    K = x.shape[-1]
+    N = W.shape[0]
+    y = np.empty(x.shape[:-1] + (N,), dtype=np.float32)
+    lib().xo_linear(_p(x), _p(W), _p(bias), _p(y), ctypes.c_long(x.size // K), ctypes.c_int(N), ctypes.c_int(K))
+    return y
+
+
 def swiglu(g, u):
     g, u = _c(g), _c(u)
     y = np.empty_like(g)

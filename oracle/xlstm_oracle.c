@@ -141,6 +141,19 @@ void xo_mlstm_output_gate(const float *h, const float *og, const float *w, float
     }
 }
 
+/* y[m,n] = sum_k x[m,k] W[n,k] + bias[n]: nn.Linear as the reference's cells call it
+ * (mlstm_projection_cell.py:85-96, mlstm_output_cell.py:84-99, mlstm_block.py:198-204) */
+void xo_linear(const float *x, const float *W, const float *bias, float *y, long M, int N, int K) {
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < M * N; ++i) {
+        long m = i / N;
+        int n = (int)(i % N);
+        double acc = 0.0;
+        for (int k = 0; k < K; ++k) acc += (double)x[m * K + k] * (double)W[(long)n * K + k];
+        y[i] = (float)acc + (bias ? bias[n] : 0.0f);
+    }
+}
+
 /* SwiGLU gate, mlstm_block.py:198-204: y = silu(g) * u */
 void xo_swiglu(const float *g, const float *u, float *y, long n) {
 #pragma omp parallel for schedule(static)

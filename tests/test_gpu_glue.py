@@ -182,3 +182,49 @@ def test_glue_rejects_cpu_tensors(ops):
         ops.rms_norm(torch.zeros(2, 8), None)
     with pytest.raises(RuntimeError):
         ops.swiglu(torch.zeros(2, 8), torch.zeros(2, 8))
+
+
+# ---- single-token Linear (weight-streaming pass with folded norm / residual / SwiGLU) ----------
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (1, 12304, 4096), (2, 4096, 10944), (4, 264, 520), (3, 33, 4096)])
+def test_linear_token_plain_bias_residual(ops, M, N, K):
+    rng = np.random.default_rng(M * 7 + N + K)
+    x = bf(rng.standard_normal((M, K)).astype(np.float32))
+    W = bf((rng.standard_normal((N, K)) * 0.05).astype(np.float32))
+    b = bf((rng.standard_normal(N) * 0.1).astype(np.float32))
+    r = bf(rng.standard_normal((M, N)).astype(np.float32))
+    t = torch.bfloat16
+    ref = xo.linear(x, W, b)
+    y = ops.linear_token(dev(W, t), dev(x, t), bias=dev(b, t))
+    assert y.shape == (M, N) and relerr(host(y), ref) <= BF16_TOL
+    y0 = ops.linear_token(dev(W, t), dev(x, t))
+    assert relerr(host(y0), xo.linear(x, W)) <= BF16_TOL
+    yr = ops.linear_token(dev(W, t), dev(x, t), bias=dev(b, t), residual=dev(r, t))
+    assert relerr(host(yr), bf(ref) + r) <= BF16_TOL
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 10944, 4096), (2, 320, 256), (4, 64, 4096)])
+def test_linear_token_norm_and_swiglu(ops, M, F, K):
+    rng = np.random.default_rng(M + F + K)
+    x = bf(rng.standard_normal((M, K)).astype(np.float32) * 3.0)
+    nw = bf(rng.uniform(0.5, 1.5, K).astype(np.float32))
+    W = bf((rng.standard_normal((2 * F, K)) * 0.05).astype(np.float32))
+    t = torch.bfloat16
+    xn = bf(xo.rmsnorm(x, nw, 1e-6))
+    # norm folded into the projection
+    y = ops.linear_token(dev(W[:F], t), dev(x, t), norm_weight=dev(nw, t), norm_eps=1e-6)
+    assert relerr(host(y), xo.linear(xn, W[:F])) <= BF16_TOL
+    # ... and the SwiGLU gate on the two stacked up projections
+    g, u = bf(xo.linear(xn, W[:F])), bf(xo.linear(xn, W[F:]))
+    act = ops.linear_token(dev(W, t), dev(x, t), norm_weight=dev(nw, t), norm_eps=1e-6, swiglu_pair=True)
+    assert act.shape == (M, F) and relerr(host(act), xo.swiglu(g, u)) <= BF16_TOL
+    # equals the separate kernels up to bf16 rounding of the same intermediate values
+    sep = ops.swiglu(*torch.nn.functional.linear(ops.rms_norm(dev(x, t), dev(nw, t), 1e-6), dev(W, t)).split(F, dim=-1))
+    assert relerr(host(act), host(sep)) <= BF16_TOL
+
+
+def test_linear_token_rejects_what_it_does_not_do(ops):
+    t = torch.bfloat16
+    with pytest.raises(ValueError):
+        ops.linear_token(torch.zeros(8, 16, device="cuda", dtype=t), torch.zeros(5, 16, device="cuda", dtype=t))
+    with pytest.raises(TypeError):
+        ops.linear_token(torch.zeros(8, 16, device="cuda"), torch.zeros(1, 16, device="cuda"))

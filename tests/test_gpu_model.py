@@ -158,3 +158,29 @@ def test_fused_projections_keep_names_values_and_results(tiny_model, golden):
         moved = moved.to("cuda:0", torch.float32)   # same dtype and device: storage is kept, still fused
         y2, _ = moved(x, None)
         assert relerr(host(y2), g["block0_out"]) < TOL
+
+
+def test_single_token_fused_block_path_bf16(tiny_model):
+    """bf16 + fused weights: a one-token call runs the six-launch path (Linear layers as
+    weight-streaming kernels with norm / residual / SwiGLU folded in); it must agree with the same
+    block stepping through the separate kernels, for 1 and for 3 sequences, carrying the state."""
+    import copy
+    model, _ = tiny_model
+    blk = copy.deepcopy(model.blocks[0]).to(torch.bfloat16)
+    for m in blk.modules():
+        if hasattr(m, "compute_dtype"):
+            m.compute_dtype = torch.bfloat16
+    ref = copy.deepcopy(blk)
+    blk.fuse_projections()
+    torch.manual_seed(5)
+    for B in (1, 3):
+        x = torch.randn(B, 9, 256, device="cuda").to(torch.bfloat16)
+        assert blk._token_step_ok(x[:, :1]) and not ref._token_step_ok(x[:, :1])
+        s1 = s2 = None
+        with torch.inference_mode():
+            for t in range(9):
+                y1, s1 = blk(x[:, t:t + 1], s1)
+                y2, s2 = ref(x[:, t:t + 1], s2)
+                assert relerr(host(y1), host(y2)) < 2e-2
+            for a, b in zip(s1, s2):
+                assert relerr(host(a), host(b)) < 2e-2

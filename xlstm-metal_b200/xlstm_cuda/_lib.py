@@ -36,6 +36,7 @@ _SIGNATURES = {
     "xlstm_add_rms_norm": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_float, c_int, c_void_p]),
     "xlstm_mlstm_output_gate": (c_int, [c_void_p] * 4 + [c_int] * 4 + [ctypes.POINTER(c_int64), c_int64, c_float, c_int, c_void_p]),
     "xlstm_swiglu": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int64, c_int, c_void_p]),
+    "xlstm_linear_token": (c_int, [c_void_p] * 4 + [c_float, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p]),
     "xlstm_causal_conv1d": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_void_p]),
 }
 

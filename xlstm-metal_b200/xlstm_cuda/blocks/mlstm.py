@@ -298,7 +298,37 @@ class mLSTMBlock(nn.Module):
         self.compute_dtype = compute_dtype
         self.state_dtype = state_dtype
 
+    def _token_step(self, x: torch.Tensor, state: Optional[State]):
+        """Single-token path (at most 4 sequences, bf16, fused weights): every Linear is one
+        weight-streaming kernel with its norm / bias / residual / SwiGLU folded in, so a block is six
+        launches: projections, cell step, output epilogue, out-projection, FFN up, FFN down."""
+        cell = self.mlstm_cell
+        W, b = cell._fused_weights()
+        B = x.shape[0]
+        NH, dqk, dv = cell.num_heads, cell.qk_dim_per_head, cell.v_dim_per_head
+        x2 = x.reshape(B, -1)
+        y = ops.linear_token(W, x2, bias=b, norm_weight=self.norm_mlstm.weight, norm_eps=self.norm_mlstm.eps)
+        o_k, o_v, o_g, o_o = NH * dqk, 2 * NH * dqk, 2 * NH * dqk + NH * dv, 2 * NH * dqk + NH * dv + 2 * NH
+        q, k, v = y[:, :o_k].view(B, NH, dqk), y[:, o_k:o_v].view(B, NH, dqk), y[:, o_v:o_g].view(B, NH, dv)
+        rk = cell.recurrent_kernel
+        h, new_state = ops.mlstm_step(q, k, v, y[:, o_g:o_g + NH], y[:, o_g + NH:o_o], state, rk.eps,
+                                      inplace=rk.inplace_state, gate_cap=cell.projection_cell.gate_soft_cap)
+        oc = cell.output_cell
+        gated = ops.mlstm_output_gate(h.unsqueeze(2), y[:, o_o:].unsqueeze(1), oc.norm.weight, oc.norm.eps)
+        x1 = ops.linear_token(oc.out_proj.weight, gated.reshape(B, -1), bias=oc.out_proj.bias, residual=x2)
+        act = ops.linear_token(self._fused_ffn(), x1, norm_weight=self.norm_ffn.weight, norm_eps=self.norm_ffn.eps,
+                               swiglu_pair=True)
+        x3 = ops.linear_token(self.ffn_proj_down.weight, act, bias=self.ffn_proj_down.bias, residual=x1)
+        return x3.view_as(x), rk._cast_state(new_state)
+
+    def _token_step_ok(self, x: torch.Tensor) -> bool:
+        return (x.shape[1] == 1 and x.shape[0] <= ops.LINEAR_TOKEN_MAX_ROWS and x.dtype == torch.bfloat16 and
+                self.mlstm_cell._fused_weights() is not None and self._fused_ffn() is not None and
+                self.mlstm_cell.compute_dtype == torch.bfloat16)
+
     def forward(self, x: torch.Tensor, state: Optional[State] = None):
+        if self._token_step_ok(x):
+            return self._token_step(x, state)
         mlstm_out, new_state = self.mlstm_cell(self.norm_mlstm(x), state)
         x, xn = ops.add_rms_norm(x, mlstm_out, self.norm_ffn.weight, self.norm_ffn.eps)   # residual + pre-norm
         fused = self._fused_ffn()

@@ -244,8 +244,16 @@ def mlstm_output_gate(h: torch.Tensor, ogate: torch.Tensor, weight: Optional[tor
     if h.stride(3) != 1:
         h = h.contiguous()
     og = ogate.to(h.dtype)
-    ld = og.stride(1) if og.dim() == 3 else NH * dv
-    if og.dim() != 3 or og.stride(2) != 1 or (B > 1 and og.stride(0) != S * ld) or ld < NH * dv:
+    ok = og.dim() == 3 and og.stride(2) == 1
+    ld = NH * dv
+    if ok:   # rows (b, s) must sit at a constant pitch: row = b * S + s
+        if S == 1:
+            ld = og.stride(0) if B > 1 else NH * dv
+        else:
+            ld = og.stride(1)
+            ok = B == 1 or og.stride(0) == S * ld
+        ok = ok and ld >= NH * dv
+    if not ok:
         og = og.contiguous()
         ld = NH * dv
     w = None if weight is None else weight.to(h.dtype).contiguous()
@@ -295,3 +303,34 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
                                                y.data_ptr(), B, S, C, K, int(bool(silu)), _dtype_code(xc), _stream()),
                "xlstm_causal_conv1d")
     return (y, st_out) if return_state else y
+
+
+LINEAR_TOKEN_MAX_ROWS = 4
+
+
+def linear_token(weight: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 1e-6,
+                 residual: Optional[torch.Tensor] = None, swiglu_pair: bool = False) -> torch.Tensor:
+    """``nn.Linear`` for up to 4 token rows as one weight-streaming pass (bf16).  ``x: [..., K]`` with at
+    most 4 rows, ``weight: [N, K]``.  Optional RMSNorm of ``x`` first (``norm_weight``), optional
+    ``residual + (...)``, or ``swiglu_pair``: ``weight`` holds gate rows then up rows (``[2F, K]``) and
+    the result is ``silu(gate) * up`` of width ``F``."""
+    _need_cuda(weight, x, bias, norm_weight, residual)
+    if weight.dtype != torch.bfloat16:
+        raise TypeError("linear_token is a bf16 kernel")
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K).to(torch.bfloat16).contiguous()
+    M = x2.shape[0]
+    if M > LINEAR_TOKEN_MAX_ROWS:
+        raise ValueError(f"linear_token takes at most {LINEAR_TOKEN_MAX_ROWS} rows, got {M}")
+    w = weight if weight.is_contiguous() else weight.contiguous()
+    rows = w.shape[0]
+    N = rows // 2 if swiglu_pair else rows
+    b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+    nw = None if norm_weight is None else norm_weight.to(torch.bfloat16).contiguous()
+    r = None if residual is None else residual.reshape(-1, N).to(torch.bfloat16).contiguous()
+    y = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device)
+    epi = 2 if swiglu_pair else (1 if r is not None else 0)
+    _lib.check(_lib.load().xlstm_linear_token(w.data_ptr(), x2.data_ptr(), _ptr(b), _ptr(nw), float(norm_eps), _ptr(r),
+                                              y.data_ptr(), M, N, K, epi, _lib.BF16, _stream()), "xlstm_linear_token")
+    return y
