@@ -252,7 +252,8 @@ def mlstm_output_gate(h: torch.Tensor, ogate: torch.Tensor, weight: Optional[tor
         else:
             ld = og.stride(1)
             ok = B == 1 or og.stride(0) == S * ld
-        ok = ok and ld >= NH * dv
+        # 16-byte accesses: the column block must start on and keep a 16-byte pitch
+        ok = ok and ld >= NH * dv and og.data_ptr() % 16 == 0 and (ld * og.element_size()) % 16 == 0
     if not ok:
         og = og.contiguous()
         ld = NH * dv
