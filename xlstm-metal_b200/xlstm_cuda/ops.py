@@ -256,6 +256,8 @@ def mlstm_output_gate(h: torch.Tensor, ogate: torch.Tensor, weight: Optional[tor
         ok = ok and ld >= NH * dv and og.data_ptr() % 16 == 0 and (ld * og.element_size()) % 16 == 0
     if not ok:
         og = og.contiguous()
+        if og.data_ptr() % 16:      # a dense but misaligned view (column block of a one-row GEMM output)
+            og = og.clone()
         ld = NH * dv
     w = None if weight is None else weight.to(h.dtype).contiguous()
     y = torch.empty(B, S, NH * dv, dtype=h.dtype, device=h.device)
