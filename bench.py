@@ -504,6 +504,32 @@ def run_glue(torch, ops, device):
     leg("swiglu", f"silu(gate)*up, two column blocks of [{rows},{2 * f}] bf16", 3 * rows * f * 2,
         lambda: ops.swiglu(gu[:, :f], gu[:, f:]))
     del gu
+    # single-token Linear (weight streaming): a ring of weight matrices larger than L2, one call per matrix
+    for name, N, K, kw in (("linear_token_qkvifo", 12304, 4096, "norm"), ("linear_token_out_proj", 4096, 4096, "res"),
+                           ("linear_token_ffn_up_swiglu", 21888, 4096, "swiglu"), ("linear_token_ffn_down", 4096, 10944, "res")):
+        ring = max(2, int(2.5e8 // (N * K * 2)) + 1)
+        Ws = [torch.randn(N, K, device=device).to(bf) * 0.02 for _ in range(ring)]
+        xv = torch.randn(1, K, device=device).to(bf)
+        nw = torch.ones(K, device=device, dtype=bf)
+        No = N // 2 if kw == "swiglu" else N
+        res = torch.randn(1, No, device=device).to(bf)
+
+        def call(kw=kw, Ws=Ws, xv=xv, nw=nw, res=res):
+            for W in Ws:
+                if kw == "norm":
+                    ops.linear_token(W, xv, norm_weight=nw)
+                elif kw == "res":
+                    ops.linear_token(W, xv, residual=res)
+                else:
+                    ops.linear_token(W, xv, norm_weight=nw, swiglu_pair=True)
+
+        call()
+        ms = _time_cuda(torch, call, 3) / ring
+        gbs = N * K * 2 / (ms * 1e-3) / 1e9
+        out[name] = {"workload": f"one token, W [{N},{K}] bf16 ({kw}), ring of {ring} matrices > L2", "ms": ms,
+                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                                  "peak_source": which}}
+        del Ws
     Bc, Sc, C = 32, 4096, 1024
     xc = torch.randn(Bc, Sc, C, device=device).to(bf)
     wc = torch.randn(C, 4, device=device).to(bf)
