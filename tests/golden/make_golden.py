@@ -56,7 +56,7 @@ def rel(a, b):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     ref = Path(args.reference)
     tn = ref / "xlstm_metal" / "torch_native" / "blocks"

@@ -28,7 +28,7 @@ from make_golden_model import apply_shims  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     ref = Path(ap.parse_args().reference)
     torch.set_grad_enabled(False)
     apply_shims(ref)

@@ -86,7 +86,7 @@ def apply_shims(ref: Path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     ref = Path(ap.parse_args().reference)
     torch.set_grad_enabled(False)
     apply_shims(ref)
