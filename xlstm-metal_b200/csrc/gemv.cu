@@ -11,7 +11,10 @@
 namespace xl {
 namespace {
 
-constexpr int GV_THREADS = 256;
+#ifndef XL_GV_THREADS
+#define XL_GV_THREADS 256
+#endif
+constexpr int GV_THREADS = XL_GV_THREADS;
 constexpr int GV_MAXM = 4;
 
 __device__ __forceinline__ void unpack8(const uint4 &u, float *f) {
@@ -73,7 +76,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const __nv_bfloat16 *_
                                                           const __nv_bfloat16 *__restrict__ residual,
                                                           __nv_bfloat16 *__restrict__ y, int N, int K) {
     extern __shared__ __align__(16) unsigned char gv_smem[];
-    __nv_bfloat16 *sx = reinterpret_cast<__nv_bfloat16 *>(gv_smem);   // [M][K]
+    const __nv_bfloat16 *sx = reinterpret_cast<const __nv_bfloat16 *>(gv_smem);   // [M][K] normalised rows
     __shared__ float s_part[M][GV_THREADS / 32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nvec = K >> 3;
@@ -118,14 +121,13 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const __nv_bfloat16 *_
                     __nv_bfloat162 pk = __floats2bfloat162_rn(xf[2 * e] * inv[m] * wf[2 * e], xf[2 * e + 1] * inv[m] * wf[2 * e + 1]);
                     o[e] = *reinterpret_cast<uint32_t *>(&pk);
                 }
-                *reinterpret_cast<uint4 *>(sx + (size_t)m * K + (size_t)v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<uint4 *>(gv_smem + ((size_t)m * K + (size_t)v * 8) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
+        __syncthreads();
     } else {
-        for (int v = tid; v < nvec * M; v += GV_THREADS)
-            reinterpret_cast<uint4 *>(sx)[v] = reinterpret_cast<const uint4 *>(x)[v];
+        sx = const_cast<__nv_bfloat16 *>(x);   // nothing to prepare: the rows are read through L1 as they are
     }
-    __syncthreads();
 
     // ---- one warp per output row (per gate/up pair for the SwiGLU epilogue), rows by grid stride
     const int total_warps = gridDim.x * (GV_THREADS / 32);
