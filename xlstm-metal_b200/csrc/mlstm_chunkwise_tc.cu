@@ -78,16 +78,16 @@ constexpr int GP_THREADS = 256;
 constexpr double RESCALE_AT = 30.0;   // rescale C~ when the frame exponent would exceed e^30
 
 template <typename T>
-__device__ __forceinline__ void gate_tile_scan(const T *ip, const T *fp, int64_t sg_s, int c, int lane, double (&bcum)[4],
-                                               double (&u)[4], double (&pmax)[4], double &excl_max, double &G,
-                                               double &U) {
+__device__ __forceinline__ void gate_tile_scan(const T *ip, const T *fp, int64_t sg_s, float cap, int c, int lane,
+                                               double (&bcum)[4], double (&u)[4], double (&pmax)[4], double &excl_max,
+                                               double &G, double &U) {
     const int t0 = c * LT + lane * 4;
     float iv[4];
     double run = 0.0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-        iv[e] = Elem<T>::ld(ip + (int64_t)(t0 + e) * sg_s);
-        run += (double)logsigmoid(Elem<T>::ld(fp + (int64_t)(t0 + e) * sg_s));
+        iv[e] = gate_softcap(Elem<T>::ld(ip + (int64_t)(t0 + e) * sg_s), cap);
+        run += (double)logsigmoid(gate_softcap(Elem<T>::ld(fp + (int64_t)(t0 + e) * sg_s), cap));
         bcum[e] = run;
     }
     double incl = run;
@@ -121,7 +121,7 @@ template <typename T>
 __global__ void __launch_bounds__(GP_THREADS)
 mlstm_gate_prep_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64_t sg_b, int64_t sg_h, int64_t sg_s,
                        const float *__restrict__ m0, float *__restrict__ gates, float *__restrict__ m_out, int NH,
-                       int NCH, float qscale) {
+                       int NCH, float qscale, float cap) {
     extern __shared__ double s_gp[];   // [NCH] each: G, U (-> m before the tile), rho before the tile, C multiplier
     double *sG = s_gp, *sU = s_gp + NCH, *sRho = s_gp + 2 * NCH, *sMul = s_gp + 3 * NCH;
     const int bh = blockIdx.x, b = bh / NH, hd = bh % NH;
@@ -130,7 +130,7 @@ mlstm_gate_prep_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64
     const T *fp = fg + b * sg_b + hd * sg_h;
     double bcum[4], u[4], pmax[4], excl, G, U;
     for (int c = warp; c < NCH; c += nwarp) {
-        gate_tile_scan<T>(ip, fp, sg_s, c, lane, bcum, u, pmax, excl, G, U);
+        gate_tile_scan<T>(ip, fp, sg_s, cap, c, lane, bcum, u, pmax, excl, G, U);
         if (lane == 0) { sG[c] = G; sU[c] = U; }
     }
     __syncthreads();
@@ -153,7 +153,7 @@ mlstm_gate_prep_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64
     }
     __syncthreads();
     for (int c = warp; c < NCH; c += nwarp) {
-        gate_tile_scan<T>(ip, fp, sg_s, c, lane, bcum, u, pmax, excl, G, U);
+        gate_tile_scan<T>(ip, fp, sg_s, cap, c, lane, bcum, u, pmax, excl, G, U);
         const double m = sU[c], rho_in = sRho[c], rho_out = sG[c];
         const double x_last = fmax(U, m);
         const double carry = fmax(excl, m);
@@ -784,7 +784,7 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
             return XLSTM_ERR_CUDA;
         gk<<<BH, GP_THREADS, gsm, st>>>(static_cast<const __nv_bfloat16 *>(p.ig), static_cast<const __nv_bfloat16 *>(p.fg),
                                         p.sg[0], p.sg[1], p.sg[2], p.C0 ? p.m0 : nullptr, gates, tail ? tail_m : p.m1,
-                                        p.NH, nch, p.qscale);
+                                        p.NH, nch, p.qscale, p.gate_cap);
     }
     if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
 
