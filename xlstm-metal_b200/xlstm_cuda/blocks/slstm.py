@@ -291,8 +291,11 @@ class sLSTMBlockDiag(nn.Module):
         xs = x.unsqueeze(1) if single else x
         B, S, _ = xs.shape
         xn = self.inp_norm(xs)
-        # gate order of the kernel: i, f, z, o
-        gx = torch.stack([self.W_i(xn), self.W_f(xn), self.W_z(xn), self.W_o(xn)], dim=2)
+        # gate order of the kernel: i, f, z, o.  One GEMM over the four stacked input projections writes
+        # gx [B,S,4,D] directly (no stack copy of four [B,S,D] results)
+        Wg = torch.cat([self.W_i.weight, self.W_f.weight, self.W_z.weight, self.W_o.weight], dim=0)
+        bg = torch.cat([self.W_i.bias, self.W_f.bias, self.W_z.bias, self.W_o.bias], dim=0)
+        gx = F.linear(xn, Wg, bg).view(B, S, 4, self.hidden_dim)
         Rs, rbs = zip(*(lin.stacked() for lin in (self.R_i, self.R_f, self.R_z, self.R_o)))
         R, rb = torch.stack(Rs), torch.stack(rbs)
         hs, state = ops.slstm_recurrent(gx, R, rb, hidden_state, self.head_num, self.config.gate_soft_cap)
