@@ -35,6 +35,23 @@ __device__ __forceinline__ void row_dot(const __nv_bfloat16 *__restrict__ wrow, 
     const int nvec = K >> 3;
     const uint4 *wv = reinterpret_cast<const uint4 *>(wrow);
     int v = lane;
+    for (; v + 224 < nvec; v += 256) {         // eight 16-byte loads of the row in flight
+        uint4 w8[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) w8[u] = wv[v + 32 * u];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            float wf[8];
+            unpack8(w8[u], wf);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                float xf[8];
+                unpack8(*reinterpret_cast<const uint4 *>(sx + (size_t)m * K + (size_t)(v + 32 * u) * 8), xf);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[m] = fmaf(wf[e], xf[e], acc[m]);
+            }
+        }
+    }
     for (; v + 96 < nvec; v += 128) {          // four 16-byte loads of the row in flight
         uint4 w4[4];
 #pragma unroll
