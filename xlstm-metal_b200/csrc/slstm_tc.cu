@@ -24,16 +24,21 @@ namespace {
 using namespace tc;
 
 constexpr int TCR_THREADS = 512;
-constexpr int TCR_NB = 32;     // batch rows per cluster = N of the MMA
 constexpr int TCR_U = 64;      // units per CTA
 constexpr int TCR_DH = 256;    // head dimension = K of the MMA
 constexpr int TCR_CL = 4;      // CTAs per cluster
-constexpr int TCR_PAD = 33;    // row pitch of the accumulator staging (floats): conflict-free both ways
-constexpr uint32_t TCR_BBOX = TCR_NB * 128;              // one 64-column box of h: 32 rows x 128 B
-constexpr uint32_t TCR_BBUF = (TCR_DH / 64) * TCR_BBOX;  // 16 KB
-constexpr uint32_t TCR_OFF_PRE = 2 * TCR_BBUF;
-constexpr uint32_t TCR_OFF_BAR = TCR_OFF_PRE + 4 * TCR_U * TCR_PAD * 4;
-constexpr uint32_t TCR_SMEM = TCR_OFF_BAR + 64;
+// NB = batch rows per cluster = N of the MMA (16 or 32): fewer rows per cluster spread the gating, which is
+// bound by the special-function units of an SM, over more SMs
+template <int NB> struct TcrCfg {
+    static constexpr int CPT = TCR_U * NB / TCR_THREADS;     // cells per thread: adjacent units of one batch row
+    static constexpr int GPW = 32 / NB;                      // batch-row groups per warp
+    static constexpr int PAD = NB + 1;                       // row pitch of the accumulator staging (floats)
+    static constexpr uint32_t BBOX = NB * 128;               // one 64-column box of h: NB rows x 128 B
+    static constexpr uint32_t BBUF = (TCR_DH / 64) * BBOX;   // 16 KB at NB = 32
+    static constexpr uint32_t OFF_PRE = 2 * BBUF;
+    static constexpr uint32_t OFF_BAR = OFF_PRE + 4 * TCR_U * PAD * 4;
+    static constexpr uint32_t SMEM = OFF_BAR + 64;
+};
 
 #ifdef XL_TCR_TRACE
 __device__ long long g_tcr_trace[64 * 16];
@@ -50,6 +55,13 @@ __device__ __forceinline__ float rcp_fast(float x) {
     return y;
 }
 __device__ __forceinline__ float tanh_fast(float x) { return 1.0f - 2.0f * rcp_fast(1.0f + __expf(2.0f * x)); }
+// one special-function op (max relative error 2^-11): used where the result is a bounded activation
+// (cell input, output gate), not where it feeds an exponent (the soft-capped gates)
+__device__ __forceinline__ float tanh_sfu(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float sigmoid_fast(float x) { return rcp_fast(1.0f + __expf(-x)); }
 
 // shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank`
@@ -64,12 +76,16 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster, uint32_t
                  ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster) : "memory");
 }
 
+template <int NB>
 __global__ void __launch_bounds__(TCR_THREADS, 1)
 slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloat16 *__restrict__ R,
                           const float *__restrict__ rb, const float *__restrict__ c0, const float *__restrict__ n0,
                           const float *__restrict__ h0, const float *__restrict__ m0, __nv_bfloat16 *__restrict__ hs,
                           float *__restrict__ c1, float *__restrict__ n1, float *__restrict__ h1, float *__restrict__ m1,
                           int B, int S, int NH, float cap) {
+    using CF = TcrCfg<NB>;
+    constexpr int CPT = CF::CPT, TCR_NB = NB, TCR_PAD = CF::PAD;
+    constexpr uint32_t TCR_BBOX = CF::BBOX, TCR_BBUF = CF::BBUF, TCR_OFF_PRE = CF::OFF_PRE, TCR_OFF_BAR = CF::OFF_BAR;
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int hd = blockIdx.y, b0 = blockIdx.z * TCR_NB;
@@ -124,38 +140,53 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
         const float hv = (h0 && b0 + b2 < B) ? h0[(size_t)(b0 + b2) * D + hd * TCR_DH + kx] : 0.f;
         *reinterpret_cast<__nv_bfloat16 *>(smem + (kx >> 6) * TCR_BBOX + sw128_off(b2, kx & 63)) = __float2bfloat16_rn(hv);
     }
-    // ---- cells owned by this thread: batch row bb = lane, the 4 adjacent units uq .. uq + 3 (warp = chunk):
-    //      8-byte accesses for the gate inputs, the h output and this CTA's part of the next B buffer
-    const int bb = lane, uq = warp * 4;
+    // ---- cells owned by this thread: batch row bb, the CPT adjacent units uq .. uq + CPT - 1:
+    //      one 8- or 4-byte access each for the gate inputs, the h output and this CTA's part of the next B buffer
+    const int bb = lane % NB, uq = (warp * CF::GPW + lane / NB) * CPT;
     const bool row_ok = b0 + bb < B;
     const size_t so = row_ok ? (size_t)(b0 + bb) * D + hd * TCR_DH + u0 + uq : 0;
-    float sc[4], sn[4], sm[4], shl[4];
+    float sc[CPT], sn[CPT], sm[CPT], shl[CPT];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < CPT; ++e) {
         const bool ok = c0 != nullptr && row_ok;
         sc[e] = ok ? c0[so + e] : 0.f;
         sn[e] = ok ? n0[so + e] : 1.f;
         sm[e] = ok ? m0[so + e] : 0.f;
         shl[e] = ok ? h0[so + e] : 0.f;
     }
-    float bias[4][4];
+    float bias[4][CPT];
 #pragma unroll
     for (int g = 0; g < 4; ++g)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) bias[g][e] = rb[(size_t)g * D + hd * TCR_DH + u0 + uq + e];
+        for (int e = 0; e < CPT; ++e) bias[g][e] = rb[(size_t)g * D + hd * TCR_DH + u0 + uq + e];
     fence_proxy_async_smem();
     tc_fence_before_sync();
     cluster.sync();   // barriers initialised, R in TMEM and B[0] complete in every CTA before any peer copy can land
 
     constexpr uint32_t IDESC = idesc_bf16(128, TCR_NB, false, false);
-    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+    const bool capped = cap > 0.f;
+    const float inv_cap = capped ? 1.0f / cap : 0.f;
     const uint64_t dB0 = smem_desc_sw128(smem_u32(smem), 0, 1024);
     const __nv_bfloat16 *gxb = gx + (size_t)hd * TCR_DH + u0 + uq;
     // input-side pre-activations of the owned cells, fetched one step ahead of their use
-    uint2 gnext[4];
+    uint32_t gnext[4][CPT / 2];
 #pragma unroll
     for (int g = 0; g < 4; ++g)
-        gnext[g] = row_ok ? *reinterpret_cast<const uint2 *>(gxb + (((size_t)(b0 + bb) * S + 0) * 4 + g) * D) : make_uint2(0u, 0u);
+#pragma unroll
+        for (int w2 = 0; w2 < CPT / 2; ++w2) gnext[g][w2] = 0u;
+    auto load_gx = [&](int tt) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const __nv_bfloat16 *src = gxb + (((size_t)(b0 + bb) * S + tt) * 4 + g) * D;
+            if constexpr (CPT == 4) {
+                const uint2 v2 = *reinterpret_cast<const uint2 *>(src);
+                gnext[g][0] = v2.x; gnext[g][CPT / 2 - 1] = v2.y;
+            } else {
+                gnext[g][0] = *reinterpret_cast<const uint32_t *>(src);
+            }
+        }
+    };
+    if (row_ok) load_gx(0);
 
     for (int t = 0; t < S; ++t) {
         const int p = t & 1;
@@ -188,21 +219,20 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
             }
         }
         TCR_TRACE(1);
-        uint2 graw[4];
+        uint32_t graw[4][CPT / 2];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) graw[g] = gnext[g];
-        if (t + 1 < S && row_ok) {
+        for (int g = 0; g < 4; ++g)
 #pragma unroll
-            for (int g = 0; g < 4; ++g)
-                gnext[g] = *reinterpret_cast<const uint2 *>(gxb + (((size_t)(b0 + bb) * S + t + 1) * 4 + g) * D);
-        }
+            for (int w2 = 0; w2 < CPT / 2; ++w2) graw[g][w2] = gnext[g][w2];
+        if (t + 1 < S && row_ok) load_gx(t + 1);
         TCR_TRACE(2);
         if (warp < 8) {
             mbar_wait(bar, (uint32_t)(t & 1), abort_flag);   // bounded; a time-out sets the flag and poisons the state below
             tc_fence_after_sync();
             TCR_TRACE(3);
-            uint32_t v[32];
-            tmem_ld32(T_D + hf * TCR_NB + lane_off, v);
+            uint32_t v[NB];
+            if constexpr (NB == 32) tmem_ld32(T_D + hf * TCR_NB + lane_off, v);
+            else tmem_ld16(T_D + hf * TCR_NB + lane_off, v);
             tmem_wait_ld();
 #pragma unroll
             for (int b2 = 0; b2 < TCR_NB; ++b2) sPre[m_row * TCR_PAD + b2] = __uint_as_float(v[b2]);
@@ -212,42 +242,76 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
         __syncthreads();
         TCR_TRACE(5);
         // gating of the owned cells; h_t to global memory and (bf16) into this CTA's box of the next B buffer
-        uint32_t hpk[2];
+        // the four cells stage by stage (all loads, then all soft-caps, ...): four independent exp /
+        // reciprocal chains in flight instead of one after the other
+        float it[CPT], ft[CPT], zt[CPT], ot[CPT];
 #pragma unroll
-        for (int e2 = 0; e2 < 2; ++e2) {
-            float hv2[2];
+        for (int e = 0; e < CPT; ++e) {
+            const uint32_t wi = graw[0][e >> 1], wf = graw[1][e >> 1], wz = graw[2][e >> 1], wo = graw[3][e >> 1];
+            const float gi = (e & 1) ? __uint_as_float(wi & 0xffff0000u) : __uint_as_float(wi << 16);
+            const float gf = (e & 1) ? __uint_as_float(wf & 0xffff0000u) : __uint_as_float(wf << 16);
+            const float gz = (e & 1) ? __uint_as_float(wz & 0xffff0000u) : __uint_as_float(wz << 16);
+            const float go = (e & 1) ? __uint_as_float(wo & 0xffff0000u) : __uint_as_float(wo << 16);
+            it[e] = sPre[(0 * 64 + uq + e) * TCR_PAD + bb] + gi + bias[0][e];
+            ft[e] = sPre[(1 * 64 + uq + e) * TCR_PAD + bb] + gf + bias[1][e];
+            zt[e] = sPre[(2 * 64 + uq + e) * TCR_PAD + bb] + gz + bias[2][e];
+            ot[e] = sPre[(3 * 64 + uq + e) * TCR_PAD + bb] + go + bias[3][e];
+        }
+        // The gating phase is bound by the special-function units (16 lanes per clock per SM, 2048 cells per
+        // CTA and step), so every cell uses as few of those ops as it can: 2 + 2 for the two soft-caps,
+        // 1 each for tanh(z) and sigmoid(o) = (1 + tanh(o/2)) / 2, ONE exponential for the pair
+        // (e^{i-m'}, e^{f+m-m'}) (one of the two is exactly 1), 1 reciprocal for c / max(n, 1).
+        float ex[CPT][2];
 #pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                const int e = 2 * e2 + x;
-                const uint32_t wi = e2 ? graw[0].y : graw[0].x, wf = e2 ? graw[1].y : graw[1].x;
-                const uint32_t wz = e2 ? graw[2].y : graw[2].x, wo = e2 ? graw[3].y : graw[3].x;
-                const float gi = x ? __uint_as_float(wi & 0xffff0000u) : __uint_as_float(wi << 16);
-                const float gf = x ? __uint_as_float(wf & 0xffff0000u) : __uint_as_float(wf << 16);
-                const float gz = x ? __uint_as_float(wz & 0xffff0000u) : __uint_as_float(wz << 16);
-                const float go = x ? __uint_as_float(wo & 0xffff0000u) : __uint_as_float(wo << 16);
-                float it = sPre[(0 * 64 + uq + e) * TCR_PAD + bb] + gi + bias[0][e];
-                float ft = sPre[(1 * 64 + uq + e) * TCR_PAD + bb] + gf + bias[1][e];
-                if (cap > 0.f) { it = cap * tanh_fast(it * inv_cap); ft = cap * tanh_fast(ft * inv_cap); }
-                const float zt = tanh_fast(sPre[(2 * 64 + uq + e) * TCR_PAD + bb] + gz + bias[2][e]);
-                const float ot = sigmoid_fast(sPre[(3 * 64 + uq + e) * TCR_PAD + bb] + go + bias[3][e]);
-                const float mt = fmaxf(ft + sm[e], it);
-                const float ie = __expf(it - mt), fe = __expf(ft - mt + sm[e]);
-                sc[e] = fmaf(fe, sc[e], ie * zt);
-                sn[e] = fmaf(fe, sn[e], ie);
-                sm[e] = mt;
-                const float hv = ot * sc[e] * rcp_fast(fmaxf(sn[e], 1.0f));
-                shl[e] = hv;
-                hv2[x] = hv;
-            }
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(hv2[0], hv2[1]);
+        for (int e = 0; e < CPT; ++e) {
+            ex[e][0] = __expf(2.0f * it[e] * inv_cap);
+            ex[e][1] = __expf(2.0f * ft[e] * inv_cap);
+            zt[e] = tanh_sfu(zt[e]);
+            ot[e] = fmaf(0.5f, tanh_sfu(0.5f * ot[e]), 0.5f);
+        }
+#pragma unroll
+        for (int e = 0; e < CPT; ++e) {
+            const float itc = cap * (1.0f - 2.0f * rcp_fast(1.0f + ex[e][0]));
+            const float ftc = cap * (1.0f - 2.0f * rcp_fast(1.0f + ex[e][1]));
+            it[e] = capped ? itc : it[e];
+            ft[e] = capped ? ftc : ft[e];
+        }
+        float mt[CPT], ie[CPT], fe[CPT];
+#pragma unroll
+        for (int e = 0; e < CPT; ++e) {
+            const float a = ft[e] + sm[e];
+            mt[e] = fmaxf(a, it[e]);
+            const float lo = __expf(-fabsf(a - it[e]));   // the smaller of the two weights; the larger is 1
+            fe[e] = a >= it[e] ? 1.0f : lo;
+            ie[e] = a >= it[e] ? lo : 1.0f;
+        }
+        float hv[CPT];
+#pragma unroll
+        for (int e = 0; e < CPT; ++e) {
+            sc[e] = fmaf(fe[e], sc[e], ie[e] * zt[e]);
+            sn[e] = fmaf(fe[e], sn[e], ie[e]);
+            sm[e] = mt[e];
+        }
+#pragma unroll
+        for (int e = 0; e < CPT; ++e) {
+            hv[e] = ot[e] * sc[e] * rcp_fast(fmaxf(sn[e], 1.0f));
+            shl[e] = hv[e];
+        }
+        uint32_t hpk[CPT / 2];
+#pragma unroll
+        for (int e2 = 0; e2 < CPT / 2; ++e2) {
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(hv[2 * e2], hv[2 * e2 + 1]);
             hpk[e2] = *reinterpret_cast<const uint32_t *>(&pk);
         }
         TCR_TRACE(8);
-        const uint2 hvec = make_uint2(hpk[0], hpk[1]);
-        if (row_ok) *reinterpret_cast<uint2 *>(hs + ((size_t)(b0 + bb) * S + t) * D + hd * TCR_DH + u0 + uq) = hvec;
+        auto store_h = [&](void *dst) {
+            if constexpr (CPT == 4) *reinterpret_cast<uint2 *>(dst) = make_uint2(hpk[0], hpk[CPT / 2 - 1]);
+            else *reinterpret_cast<uint32_t *>(dst) = hpk[0];
+        };
+        if (row_ok) store_h(hs + ((size_t)(b0 + bb) * S + t) * D + hd * TCR_DH + u0 + uq);
         if (t + 1 < S) {
             unsigned char *mybox = smem + (p ^ 1) * TCR_BBUF + rank * TCR_BBOX;
-            *reinterpret_cast<uint2 *>(mybox + sw128_off(bb, uq)) = hvec;
+            store_h(mybox + sw128_off(bb, uq));
             fence_proxy_async_smem();     // generic-proxy writes -> visible to the bulk copies and the MMAs (async proxy)
             TCR_TRACE(6);
             __syncthreads();
@@ -268,7 +332,7 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
     const bool failed = *abort_flag != 0;
     if (row_ok) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < CPT; ++e) {
             c1[so + e] = sc[e]; n1[so + e] = sn[e]; h1[so + e] = shl[e];
             m1[so + e] = failed ? __int_as_float(0x7fc00000) : sm[e];   // a device-side time-out shows as NaN state
         }
@@ -288,13 +352,18 @@ bool slstm_recurrent_tc_supported(int dtype, int dh, const void *R, const void *
 int slstm_recurrent_tc(const void *gx, const void *R, const float *rb, const float *c0, const float *n0, const float *h0,
                        const float *m0, void *hs, float *c1, float *n1, float *h1, float *m1, int B, int S, int NH,
                        float cap, cudaStream_t st) {
-    auto kern = slstm_recurrent_tc_kernel;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TCR_SMEM) != cudaSuccess)
+    // 16 batch rows per cluster while all clusters still fit on the GPU at once (the kernel is one long
+    // sequential loop: a second wave would double its time), else 32
+    const bool nb16 = (long long)TCR_CL * NH * ((B + 15) / 16) <= 148;
+    auto kern = nb16 ? slstm_recurrent_tc_kernel<16> : slstm_recurrent_tc_kernel<32>;
+    const int NBv = nb16 ? 16 : 32;
+    const uint32_t smem_bytes = nb16 ? TcrCfg<16>::SMEM : TcrCfg<32>::SMEM;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) != cudaSuccess)
         return XLSTM_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(TCR_CL, NH, (B + TCR_NB - 1) / TCR_NB);
+    cfg.gridDim = dim3(TCR_CL, NH, (B + NBv - 1) / NBv);
     cfg.blockDim = dim3(TCR_THREADS);
-    cfg.dynamicSmemBytes = TCR_SMEM;
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
