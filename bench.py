@@ -654,6 +654,7 @@ def main():
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-shaped full-model run")
     ap.add_argument("--glue-only", action="store_true",
                     help="time only the HBM-bound kernels either side of the cells (a small command to profile)")
+    ap.add_argument("--slstm-only", action="store_true", help="run only the sLSTM stack leg (BASELINE configs[4])")
     ap.add_argument("--model-only", action="store_true",
                     help="run only the 7B-shaped full-model leg (prefill 2048 + 256 decode tokens)")
     args = ap.parse_args()
@@ -661,6 +662,11 @@ def main():
         import torch
         sys.path.insert(0, str(ROOT / "xlstm-metal_b200"))
         print(json.dumps({"model": run_model(torch, torch.device("cuda:0"), 2048, 256)}))
+        return
+    if args.slstm_only:
+        import torch
+        sys.path.insert(0, str(ROOT / "xlstm-metal_b200"))
+        print(json.dumps({"slstm": run_slstm(torch, None, torch.device("cuda:0"), 1, 0)}))
         return
     if args.glue_only:
         import torch
