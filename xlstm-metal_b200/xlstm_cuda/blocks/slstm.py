@@ -299,9 +299,34 @@ class sLSTMBlockDiag(nn.Module):
         R, rb = torch.stack(Rs), torch.stack(rbs)
         hs, state = ops.slstm_recurrent(gx, R, rb, hidden_state, self.head_num, self.config.gate_soft_cap)
         out = self.hid_norm(hs)
-        a, b = self.up_proj(out).chunk(2, dim=-1)
-        out = self.down_proj(a * F.gelu(b)) + xs
+        Wu, bu, Wd, Pp = self._ffn_weights()
+        y = F.linear(out, Wu, bu)
+        out = F.linear(y[..., :Pp] * F.gelu(y[..., Pp:]), Wd, self.down_proj.bias) + xs
         return (out[:, 0] if single else out), state
+
+    def _ffn_weights(self):
+        """Gated-FFN weights with the projection width padded to a multiple of 8 (zero rows / columns):
+        ``int(4/3 * hidden)`` is odd-sized (1365 at hidden 1024), which sends both GEMMs to unaligned
+        legacy kernels several times slower; the padded product is identical.  Rebuilt when the
+        parameters change."""
+        up, down = self.up_proj, self.down_proj
+        P = down.in_features
+        Pp = (P + 7) // 8 * 8
+        if Pp == P:
+            return up.weight, up.bias, down.weight, P
+        key = (up.weight._version, up.weight.data_ptr(), up.bias._version, down.weight._version, down.weight.data_ptr(),
+               up.weight.dtype, up.weight.device)
+        cache = getattr(self, "_ffn_cache", None)
+        if cache is None or cache[0] != key:
+            with torch.no_grad():
+                Wu = up.weight.new_zeros(2 * Pp, up.in_features)
+                Wu[:P], Wu[Pp:Pp + P] = up.weight[:P], up.weight[P:]
+                bu = up.bias.new_zeros(2 * Pp)
+                bu[:P], bu[Pp:Pp + P] = up.bias[:P], up.bias[P:]
+                Wd = down.weight.new_zeros(down.out_features, Pp)
+                Wd[:, :P] = down.weight
+            self._ffn_cache = cache = (key, Wu, bu, Wd)
+        return cache[1], cache[2], cache[3], Pp
 
 
 __all__ = ["CausalConv1d", "sLSTMStepwiseKernelCell", "sLSTMProjectionCell", "sLSTMOutputCell", "sLSTMNeuron", "sLSTMBlock",
