@@ -127,7 +127,8 @@ class xLSTMRunner:
     @torch.inference_mode()
     def generate_next_token(self, input_ids: torch.Tensor, temperature: float = 1.0, top_k: Optional[int] = None,
                             top_p: Optional[float] = None) -> int:
-        next_logits = self.forward(input_ids)[0, -1, :].float()
+        logits, self.state = self.model(input_ids, self.state, return_last_states=True, last_token_only=True)
+        next_logits = soft_cap(logits, self.output_logit_soft_cap)[0, -1, :].float()
         if temperature == 0.0:  # greedy
             return int(torch.argmax(next_logits).item())
         if temperature != 1.0:

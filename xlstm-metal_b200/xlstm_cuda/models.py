@@ -57,7 +57,10 @@ class WiredxLSTM(nn.Module):
         self.lm_head = nn.Linear(d, vocab, bias=False, device=dev, dtype=dt) if st["has_lm_head"] else None
         self._apply_weight_tying()
 
-    def forward(self, input_ids: torch.Tensor, state: Optional[List[Tuple]] = None, return_last_states: bool = False):
+    def forward(self, input_ids: torch.Tensor, state: Optional[List[Tuple]] = None, return_last_states: bool = False,
+                last_token_only: bool = False):
+        """``last_token_only`` (not in the reference signature): logits of the last position only,
+        ``[B, 1, vocab]`` -- what generation consumes after a prompt; skips the ``[B, S, vocab]`` head GEMM."""
         x = input_ids.to(self.device)
         if self.embedding is not None:
             x = self.embedding(x)
@@ -67,6 +70,8 @@ class WiredxLSTM(nn.Module):
         for idx, block in enumerate(self.blocks):
             x, block_state = block(x, state[idx])
             new_states.append(block_state)
+        if last_token_only:
+            x = x[:, -1:]
         if self.out_norm is not None:
             x = self.out_norm(x)
         logits = self.lm_head(x) if self.lm_head is not None else x
