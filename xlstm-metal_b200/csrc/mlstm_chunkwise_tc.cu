@@ -231,12 +231,15 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
     return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
 }
 
-// q~ . n for all rows of the (already scaled) Q~ tile, added to s_qn.  Lane mapping: lane = (g, c) with
+// q~ . n for all rows from the RAW Q tile (before it is scaled in place): the dot product q . n is taken
+// in fp32 from the exact bf16 inputs and multiplied by the row scale afterwards, so the state part of the
+// normaliser carries no bf16 rounding of Q~ (it matters where q . n cancels).  Lane mapping: lane = (g, c) with
 // c the physical 16-byte chunk and g a row group; a warp owns the rows with (row & 7) in {2w, 2w+1}, so
 // for a fixed residue rho every lane always meets the same LOGICAL chunk c ^ rho: its 8 values of n are
 // loaded once per (rho, box) and the tile loads are 4 x 128 contiguous bytes per instruction.
 template <int DQK>
-__device__ __forceinline__ void qn_pass(const unsigned char *smem, const float *s_n, float *s_qn, int wl, int lane) {
+__device__ __forceinline__ void qn_pass(const unsigned char *smem, const float *s_n, float *s_qn, const float *row_scale,
+                                        int wl, int lane) {
     using SM = Smem<DQK>;
     constexpr int NBOX = SM::NBOX;
     const int c = lane & 7, g = lane >> 3;
@@ -270,7 +273,10 @@ __device__ __forceinline__ void qn_pass(const unsigned char *smem, const float *
             v += __shfl_xor_sync(0xffffffffu, v, 1);
             v += __shfl_xor_sync(0xffffffffu, v, 2);
             v += __shfl_xor_sync(0xffffffffu, v, 4);
-            if (c == 0) s_qn[(2 * wl + rr) + 8 * g + 32 * i] = v;
+            if (c == 0) {
+                const int row = (2 * wl + rr) + 8 * g + 32 * i;
+                s_qn[row] = v * row_scale[row];
+            }
         }
 }
 
@@ -571,13 +577,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             tc_fence_before_sync();
             mbar_arrive(&bars[B_PREADY]);
             if (t == 0) TRACE(6);
-            // q~ . n (the state part of the normaliser) from the scaled tile Q~ and the previous n:
-            // needs Q~ complete, n of the previous tile final, and the previous epilogue done with s_qn
-            if (!mbar_wait(&bars[B_QSCALED], ph, abort_flag)) break;
-            if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
-            if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
-            qn_pass<DQK>(smem, s_n, s_qn, warp - 4, lane);
-            mbar_arrive(&bars[B_QNDONE]);
             if (NHALF == 2) {  // C pass for rows [128,256) of C (the K~ warps take rows [0,128))
                 const bool last = (k == NCH - 1);
                 if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
@@ -599,6 +598,12 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             const uint32_t ph = k & 1;
             const float winq = gbase[(size_t)k * GW + G_WINQ + t];
             if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
+            // q . n from the raw tile first (Q~ is only needed by the last MMA group of the tile, so this is
+            // off the critical path): needs n of the previous tile final and the previous epilogue done with s_qn
+            if (!(k == 0 ? mbar_wait(&bars[B_CBREADY], 0, abort_flag) : mbar_wait(&bars[B_NDONE], (k - 1) & 1, abort_flag))) break;
+            if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
+            qn_pass<DQK>(smem, s_n, s_qn, gbase + (size_t)k * GW + G_WINQ, warp - 8, lane);
+            mbar_arrive(&bars[B_QNDONE]);
             if (t == 0) TRACE(9);
             scale_rows<DQK>(smem + SM::Q, t, winq);
             if (t == 0) TRACE(10);
