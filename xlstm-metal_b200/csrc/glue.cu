@@ -54,11 +54,11 @@ template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4 
 // where these kernels would otherwise be bound by instruction issue, not by HBM) the approximate
 // exp / reciprocal, whose ~2 ulp fp32 error disappears in the bf16 rounding
 template <typename T> __device__ __forceinline__ float sigmoid_t(float x) {
-    if (sizeof(T) == 2) return __frcp_rn(1.0f + __expf(-x));
+    if (sizeof(T) == 2) return __fdividef(1.0f, 1.0f + __expf(-x));
     return 1.0f / (1.0f + expf(-x));
 }
 template <typename T> __device__ __forceinline__ float silu_t(float x) {
-    if (sizeof(T) == 2) return x * __frcp_rn(1.0f + __expf(-x));
+    if (sizeof(T) == 2) return __fdividef(x, 1.0f + __expf(-x));
     return x / (1.0f + expf(-x));
 }
 
@@ -305,12 +305,15 @@ static int swiglu_launch(const void *g, const void *u, void *y, int64_t rows, in
 }
 
 // ---------------------------------------------------------------------------
-// causal depthwise conv1d (+ SiLU), channels-last.  A thread owns VN adjacent channels and walks
-// CONV_T consecutive tokens with the last K-1 inputs in registers, so every input is read once
-// (plus a K-1 halo per token block); a warp covers 32*VN adjacent channels of one token.
+// causal depthwise conv1d (+ SiLU), channels-last.  A thread owns VN adjacent channels and CONV_G
+// consecutive tokens: it issues the CONV_G + K - 1 input loads it needs at once (the K - 1 halo rows are
+// L1 hits: the neighbouring warp of the CTA loads them as its own rows), then computes its outputs; no
+// loop-carried window, so many independent loads are in flight per thread.  A warp covers 32*VN adjacent
+// channels, the four warps of a CTA four consecutive token groups (CONV_T = 32 tokens per CTA).
 // ---------------------------------------------------------------------------
-constexpr int CONV_T = 64;          // tokens per thread block: amortises the tap / halo loads
-constexpr int CONV_ALIAS_MAX = 16;  // longest call whose new state may overwrite the old one in place
+constexpr int CONV_G = 8;           // tokens per thread
+constexpr int CONV_T = 32;          // tokens per CTA (4 warps x CONV_G)
+constexpr int CONV_ALIAS_MAX = 16;  // longest call whose new state may overwrite the old one in place (one CTA per batch row)
 constexpr int CONV_KMAX = 8;
 
 template <typename T, int K>
@@ -319,61 +322,64 @@ __global__ void __launch_bounds__(128) causal_conv1d_kernel(const T *__restrict_
                                                             T *__restrict__ state_out, T *__restrict__ y, int S, int C,
                                                             int act_silu) {
     constexpr int VN = Vec16<T>::N;
-    const int cv = blockIdx.x * blockDim.x + threadIdx.x;   // channel vector
-    if (cv * VN >= C) return;
-    const int c0 = cv * VN;
+    constexpr int H = K - 1;                               // history length
+    constexpr int NIN = CONV_G + H;                        // input rows a thread reads
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cv = blockIdx.x * 32 + lane;                 // channel vector
+    const bool ch_ok = cv * VN < C;
+    const int c0 = ch_ok ? cv * VN : 0;
     const int b = blockIdx.z;
-    const int s_begin = blockIdx.y * CONV_T;
-    const int s_end = min(S, s_begin + CONV_T);
+    const int s0 = blockIdx.y * CONV_T + warp * CONV_G;    // first token of this thread
     const T *xb = x + (size_t)b * S * C + c0;
     T *yb = y + (size_t)b * S * C + c0;
-    constexpr int H = K - 1;                               // history length
-    float wk[K][VN];                                       // wk[j][e]: tap j of channel c0 + e
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    // input rows s0 - H .. s0 + CONV_G - 1; rows before token 0 come from the state (or are zero)
+    uint4 raw[NIN];
 #pragma unroll
-    for (int e = 0; e < VN; ++e)
-#pragma unroll
-        for (int j = 0; j < K; ++j) wk[j][e] = Elem<T>::ld(w + (size_t)(c0 + e) * K + j);
-    float bv[VN];
-    if (bias) ld16<T>(bias + c0, bv);
-    else
-#pragma unroll
-        for (int e = 0; e < VN; ++e) bv[e] = 0.f;
-    // win[j] = input at token s - (K-1) + j; tokens before 0 come from the state (or are zero)
-    float win[K][VN];
-#pragma unroll
-    for (int j = 0; j < H; ++j) {
-        const int t = s_begin - H + j;
-        if (t >= 0) ld16<T>(xb + (size_t)t * C, win[j]);
-        else if (state_in) ld16<T>(state_in + ((size_t)b * H + (H + t)) * C + c0, win[j]);
-        else
-#pragma unroll
-            for (int e = 0; e < VN; ++e) win[j][e] = 0.f;
+    for (int r = 0; r < NIN; ++r) {
+        const int t = s0 - H + r;
+        if (!ch_ok || t >= S) raw[r] = zero4;
+        else if (t >= 0) raw[r] = *reinterpret_cast<const uint4 *>(xb + (size_t)t * C);
+        else if (state_in) raw[r] = *reinterpret_cast<const uint4 *>(state_in + ((size_t)b * H + (H + t)) * C + c0);
+        else raw[r] = zero4;
     }
-    // the new state (last K-1 inputs of [state ; x]) is written by the block that owns the last tokens;
-    // entries that stay in the old state are read here, before anything is stored (in-place update)
-    const bool owns_state = state_out != nullptr && s_end == S;
-    float keep[K][VN];
-    if (owns_state && S < H) {
+    // the new state = last K-1 inputs of [state ; x]: written by the CTA that owns the last token, after
+    // every warp of it has read what it needs from the old state (in-place update)
+    const bool owns_state = state_out != nullptr && (int)blockIdx.y == (S - 1) / CONV_T;
+    uint4 st_new[H > 0 ? H : 1];
+    if (owns_state && warp == 0 && ch_ok) {
 #pragma unroll
         for (int j = 0; j < H; ++j) {
-            if (j < H - S) {
-                if (state_in) ld16<T>(state_in + ((size_t)b * H + (j + S)) * C + c0, keep[j]);
-                else
-#pragma unroll
-                    for (int e = 0; e < VN; ++e) keep[j][e] = 0.f;
-            }
+            const int t = S - H + j;                        // token held by state slot j
+            if (t >= 0) st_new[j] = *reinterpret_cast<const uint4 *>(xb + (size_t)t * C);
+            else if (state_in) st_new[j] = *reinterpret_cast<const uint4 *>(state_in + ((size_t)b * H + (j + S)) * C + c0);
+            else st_new[j] = zero4;
         }
     }
-    // the block's inputs are fetched in batches of 8 tokens, all loads of a batch in flight together
-    for (int s0 = s_begin; s0 < s_end; s0 += 8) {
-        uint4 raw[8];
+    if (ch_ok) {
+        // the VN x K taps of this thread's channels are VN*K contiguous elements = K 16-byte vectors
+        float wflat[VN * K];
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-            if (s0 + k < s_end) raw[k] = *reinterpret_cast<const uint4 *>(xb + (size_t)(s0 + k) * C);
+        for (int j = 0; j < K; ++j) ld16<T>(w + (size_t)c0 * K + j * VN, wflat + j * VN);
+        float wk[K][VN];                                   // wk[j][e]: tap j of channel c0 + e
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            if (s0 + k < s_end) {
-                unpack16<T>(raw[k], win[H]);
+        for (int e = 0; e < VN; ++e)
+#pragma unroll
+            for (int j = 0; j < K; ++j) wk[j][e] = wflat[e * K + j];
+        float bv[VN];
+        if (bias) ld16<T>(bias + c0, bv);
+        else
+#pragma unroll
+            for (int e = 0; e < VN; ++e) bv[e] = 0.f;
+        // every input row is unpacked once into a window of the last K rows (fully unrolled: the shifts
+        // below are register renames)
+        float win[K][VN];
+#pragma unroll
+        for (int j = 0; j < H; ++j) unpack16<T>(raw[j], win[j]);
+#pragma unroll
+        for (int g = 0; g < CONV_G; ++g) {
+            unpack16<T>(raw[g + H], win[H]);
+            if (s0 + g < S) {
                 float acc[VN];
 #pragma unroll
                 for (int e = 0; e < VN; ++e) acc[e] = bv[e];
@@ -384,25 +390,19 @@ __global__ void __launch_bounds__(128) causal_conv1d_kernel(const T *__restrict_
                 if (act_silu)
 #pragma unroll
                     for (int e = 0; e < VN; ++e) acc[e] = silu_t<T>(acc[e]);
-                st16<T>(yb + (size_t)(s0 + k) * C, acc);
-#pragma unroll
-                for (int j = 0; j < H; ++j)
-#pragma unroll
-                    for (int e = 0; e < VN; ++e) win[j][e] = win[j + 1][e];
+                st16<T>(yb + (size_t)(s0 + g) * C, acc);
             }
+#pragma unroll
+            for (int j = 0; j < H; ++j)
+#pragma unroll
+                for (int e = 0; e < VN; ++e) win[j][e] = win[j + 1][e];
         }
     }
-    if (owns_state) {
+    if (state_out != nullptr) {          // uniform over the CTA
+        __syncthreads();
+        if (owns_state && warp == 0 && ch_ok) {
 #pragma unroll
-        for (int j = 0; j < H; ++j) {
-            const int t = S - H + j;                        // token held by state slot j
-            float tmp[VN];
-            if (t >= 0) {
-                ld16<T>(xb + (size_t)t * C, tmp);
-                st16<T>(state_out + ((size_t)b * H + j) * C + c0, tmp);
-            } else {
-                st16<T>(state_out + ((size_t)b * H + j) * C + c0, keep[j]);
-            }
+            for (int j = 0; j < H; ++j) *reinterpret_cast<uint4 *>(state_out + ((size_t)b * H + j) * C + c0) = st_new[j];
         }
     }
 }
@@ -476,11 +476,12 @@ extern "C" int xlstm_causal_conv1d(const void *x, const void *w, const void *bia
     if (state_out && state_out == state_in && S > CONV_ALIAS_MAX) return XLSTM_ERR_INVALID;
     const int vn = dtype == XLSTM_F32 ? 4 : 8;
     const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(bias) |
-                         reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out);
+                         reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out) |
+                         reinterpret_cast<uintptr_t>(w);
     if (C % vn || (al & 15u) || B > 65535 || (S + CONV_T - 1) / CONV_T > 65535) return XLSTM_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int cvec = C / vn;
-    const dim3 grid((cvec + 127) / 128, (S + CONV_T - 1) / CONV_T, B);
+    const dim3 grid((cvec + 31) / 32, (S + CONV_T - 1) / CONV_T, B);
 #define XL_CONV_CASE(KK)                                                                                              \
     case KK:                                                                                                          \
         if (dtype == XLSTM_F32)                                                                                       \
