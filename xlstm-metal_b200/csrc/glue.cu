@@ -150,6 +150,65 @@ __global__ void __launch_bounds__(RN_THREADS) rms_norm_generic_kernel(const T *_
         Elem<T>::st(yr + i, Elem<T>::ld(xr + i) * inv * (w ? Elem<T>::ld(w + i) : 1.0f));
 }
 
+// Many rows: one WARP per row, the row kept as packed 16-byte vectors in registers (NV per lane), no
+// CTA barrier, rows by grid stride.  All NV loads of a row are in flight at once.
+constexpr int RW_WARPS = 8;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(RW_WARPS * 32) rms_norm_warp_kernel(const T *__restrict__ x, const T *__restrict__ r,
+                                                                     const T *__restrict__ w, T *__restrict__ sum,
+                                                                     T *__restrict__ y, int64_t rows, int cols, float eps) {
+    constexpr int VN = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int nvec = cols / VN;
+    for (int64_t row = (int64_t)blockIdx.x * RW_WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * RW_WARPS) {
+        const uint4 *xr = reinterpret_cast<const uint4 *>(x + (size_t)row * cols);
+        uint4 raw[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32 * i < nvec) raw[i] = xr[lane + 32 * i];
+        if (r) {   // residual add: s = x + r rounded to the activation type, written as the new residual stream
+            const uint4 *rr = reinterpret_cast<const uint4 *>(r + (size_t)row * cols);
+            uint4 *sr = reinterpret_cast<uint4 *>(sum + (size_t)row * cols);
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+                if (lane + 32 * i < nvec) {
+                    float a[VN], b[VN];
+                    unpack16<T>(raw[i], a);
+                    unpack16<T>(rr[lane + 32 * i], b);
+#pragma unroll
+                    for (int e = 0; e < VN; ++e) a[e] += b[e];
+                    st16<T>(reinterpret_cast<T *>(&raw[i]), a);
+                    sr[lane + 32 * i] = raw[i];
+                }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32 * i < nvec) {
+                float a[VN];
+                unpack16<T>(raw[i], a);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) ss = fmaf(a[e], a[e], ss);
+            }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)cols + eps);
+        uint4 *yr = reinterpret_cast<uint4 *>(y + (size_t)row * cols);
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + 32 * i < nvec) {
+                float a[VN], wv[VN];
+                unpack16<T>(raw[i], a);
+                if (w) ld16<T>(w + (size_t)(lane + 32 * i) * VN, wv);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) a[e] = a[e] * inv * (w ? wv[e] : 1.0f);
+                uint4 o;
+                st16<T>(reinterpret_cast<T *>(&o), a);
+                yr[lane + 32 * i] = o;
+            }
+    }
+}
+
 template <typename T>
 static int rms_norm_launch(const void *x, const void *r, const void *w, void *sum, void *y, int64_t rows, int cols,
                            float eps, cudaStream_t st) {
@@ -161,6 +220,15 @@ static int rms_norm_launch(const void *x, const void *r, const void *w, void *su
                          cols % VN == 0;
     const int nvec = cols / VN;
     const dim3 grid((unsigned)rows);
+    if (aligned && !r && rows >= 4 * 148 && nvec <= 32 * 16) {   // enough rows to give every SM several warps' worth; the
+        // residual variant stays on the CTA-per-row kernel, which measured faster for two input streams
+        const int64_t want = (rows + RW_WARPS - 1) / RW_WARPS;
+        const unsigned wg = (unsigned)(want < 148 * 8 ? want : 148 * 8);
+        if (nvec <= 32 * 4) rms_norm_warp_kernel<T, 4><<<wg, RW_WARPS * 32, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
+        else if (nvec <= 32 * 8) rms_norm_warp_kernel<T, 8><<<wg, RW_WARPS * 32, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
+        else rms_norm_warp_kernel<T, 16><<<wg, RW_WARPS * 32, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
+        return launch_status();
+    }
     if (aligned && nvec <= RN_THREADS * 1) rms_norm_kernel<T, 1><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
     else if (aligned && nvec <= RN_THREADS * 2) rms_norm_kernel<T, 2><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
     else if (aligned && nvec <= RN_THREADS * 4) rms_norm_kernel<T, 4><<<grid, RN_THREADS, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
