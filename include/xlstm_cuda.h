@@ -101,8 +101,9 @@ size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int 
  * xlstm_mlstm_chunkwise_fwd fused with the all-gather of h for head-sharded execution: the
  * epilogue stores every h tile to `h` AND, with the same strides and offsets, to `n_peers` (<= 7)
  * further base pointers - the same head slot of the peer GPUs' [B,S,NH_total,dv] buffers, mapped
- * into this process (symmetric memory / IPC).  The stores are plain 16-byte st.global over NVLink
- * and overlap the tensor-core work tile by tile; after the kernels of all ranks have finished (one
+ * into this process (symmetric memory / IPC).  Each staged h tile goes to every destination by a TMA tile store
+ * (cp.async.bulk.tensor shared -> global over NVLink; no multicast and no load from peer memory)
+ * and overlaps the tensor-core work tile by tile; after the kernels of all ranks have finished (one
  * cross-rank barrier) every rank holds the complete h and can run the out-projection on it.
  * `h_peers` is a HOST array of device pointers.  bf16, tensor-core shapes, S a multiple of 128.
  * The reference has no multi-device path (its docs say "Single-device only", docs/COMPONENTS.md:4334-4339); this stands in for the

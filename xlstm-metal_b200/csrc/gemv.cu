@@ -11,10 +11,7 @@
 namespace xl {
 namespace {
 
-#ifndef XL_GV_THREADS
-#define XL_GV_THREADS 256
-#endif
-constexpr int GV_THREADS = XL_GV_THREADS;
+constexpr int GV_THREADS = 256;
 constexpr int GV_MAXM = 4;
 
 __device__ __forceinline__ void unpack8(const uint4 &u, float *f) {

@@ -23,6 +23,10 @@ struct ChunkwiseParams {
 int mlstm_chunkwise_simt(const ChunkwiseParams &p, int dtype, cudaStream_t st);
 
 // tcgen05 / TMEM / TMA path: bf16, L == 64, dqk == 256 (or 128/64), dv % 128 == 0, whole chunks
+// shape_ok: the shape, strides and alignment fit the tensor-core kernel; driver_ok: the driver entry point
+// that encodes TMA descriptors could be resolved; supported = both
+bool mlstm_chunkwise_tc_shape_ok(const ChunkwiseParams &p, int dtype);
+bool mlstm_chunkwise_tc_driver_ok();
 bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype);
 size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L);
 int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspace_bytes, cudaStream_t st);

@@ -80,10 +80,12 @@ extern "C" int xlstm_mlstm_chunkwise_fwd_static(const void *q, const void *k, co
         p.sg[0] = nh * s; p.sg[1] = s; p.sg[2] = 1;
     }
     // the exact CUDA-core path needs no scratch at all
-    if (!xl::mlstm_chunkwise_tc_supported(p, dtype)) return xl::mlstm_chunkwise_simt(p, dtype, st);
+    if (!xl::mlstm_chunkwise_tc_shape_ok(p, dtype)) return xl::mlstm_chunkwise_simt(p, dtype, st);
 
+    // size check before anything else can launch: a problem beyond the block is an error, never a fallback
     const size_t need = xl::mlstm_chunkwise_tc_workspace(B, NH, S, dqk, dv, L);
-    if (need > XLSTM_STATIC_SCRATCH_BYTES) return XLSTM_ERR_STATIC_SCRATCH;  // problem larger than the built-in block
+    if (need > XLSTM_STATIC_SCRATCH_BYTES) return XLSTM_ERR_STATIC_SCRATCH;
+    if (!xl::mlstm_chunkwise_tc_driver_ok()) return XLSTM_ERR_CUDA;
     void *scratch = nullptr;
     const int rc = scratch_for_current_device(&scratch);
     if (rc != XLSTM_OK) return rc;

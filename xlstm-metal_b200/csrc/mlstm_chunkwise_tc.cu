@@ -47,13 +47,6 @@ constexpr int G_U2 = 0, G_X2 = LT, G_WINQ = 2 * LT, G_W = 3 * LT, G_EMT = 4 * LT
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr size_t WS_HEADER = 256;  // status word lives in the first bytes of the scratch
 
-#ifdef XL_TC_TRACE
-__device__ long long g_trace[64 * 32];
-#define TRACE(id) do { if (blockIdx.x == 0 && blockIdx.y == 0 && k < 64) g_trace[k * 32 + (id)] = clock64(); } while (0)
-#else
-#define TRACE(id) do { } while (0)
-#endif
-
 struct TcParams {
     CUtensorMap tq, tk, tv;
     const float *gates;            // [B*NH][NCH][GW]
@@ -433,16 +426,13 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 const int t0 = k * LT;
                 if (k > 0 && !(mbar_wait(&bars[B_UPDDONE], (k - 1) & 1, abort_flag) &&
                                mbar_wait(&bars[B_KREAD], (k - 1) & 1, abort_flag))) break;
-                TRACE(17);
                 mbar_expect_tx(&bars[B_KFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::K + q * SM::BOX, &p.tk, &bars[B_KFULL], q * 64, t0, hd, b);
                 if (k > 0 && !(mbar_wait(&bars[B_H1DONE], (k - 1) & 1, abort_flag) &&
                                mbar_wait(&bars[B_QNDONE], (k - 1) & 1, abort_flag))) break;
-                TRACE(16);
                 mbar_expect_tx(&bars[B_QFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[B_QFULL], q * 64, t0, hd, b);
                 if (k > 0 && !mbar_wait(&bars[B_VFREE], (k - 1) & 1, abort_flag)) break;   // h tile staged in V has been stored
-                TRACE(18);
                 mbar_expect_tx(&bars[B_VFULL], 2 * SM::BOX);
                 for (int q = 0; q < 2; ++q) tma_load_4d(smem + SM::V + q * SM::BOX, &p.tv, &bars[B_VFULL], col0 + q * 64, t0, hd, b);
             }
@@ -461,11 +451,9 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             const uint64_t dV = smem_desc_sw128(smem_u32(smem + SM::V), SM::BOX, 1024);
             for (int k = 0; k < NCH; ++k) {
                 const uint32_t ph = k & 1;
-                TRACE(0);
                 // S = Q K^T  (the previous tile's P V, issued earlier, finishes first: in-order pipe)
                 if (!(mbar_wait(&bars[B_QFULL], ph, abort_flag) && mbar_wait(&bars[B_KFULL], ph, abort_flag))) break;
                 tc_fence_after_sync();
-                TRACE(1);
 #pragma unroll
                 for (int kk = 0; kk < DQK / 16; ++kk) {
                     const uint32_t o = ((kk >> 2) * SM::BOX + (kk & 3) * 32) >> 4;
@@ -477,7 +465,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 if (!(mbar_wait(&bars[B_KSCALED], ph, abort_flag) && mbar_wait(&bars[B_VFULL], ph, abort_flag) &&
                       mbar_wait(&bars[B_CBREADY], ph, abort_flag))) break;
                 tc_fence_after_sync();
-                TRACE(3);
 #pragma unroll
                 for (int hf = 0; hf < NHALF; ++hf)
 #pragma unroll
@@ -488,14 +475,12 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 if (!mbar_wait(&bars[B_PREADY], ph, abort_flag)) break;
                 if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
                 tc_fence_after_sync();
-                TRACE(4);
 #pragma unroll
                 for (int kk = 0; kk < LT / 16; ++kk) mma_ts(T_H, T_S + kk * 8, dV + kk * (2048 >> 4), ID_KM, kk > 0);
                 mma_commit(&bars[B_H2DONE]);
                 // H += Q~ Cb   (Q~ scaled in place; Cb from the previous C pass)
                 if (!mbar_wait(&bars[B_QSCALED], ph, abort_flag)) break;
                 tc_fence_after_sync();
-                TRACE(2);
 #pragma unroll
                 for (int kk = 0; kk < DQK / 16; ++kk) {
                     const uint32_t o = ((kk >> 2) * SM::BOX + (kk & 3) * 32) >> 4;
@@ -542,7 +527,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             for (int pc = 0; pc < 4; ++pc) u2v[pc] = g[G_U2 + pc * 32 + lane];
             if (!mbar_wait(&bars[B_SDONE], ph, abort_flag)) break;
             tc_fence_after_sync();
-            if (t == 0) TRACE(5);
             float rowsum = 0.f;
 #pragma unroll
             for (int pc = 0; pc < 4; ++pc) {
@@ -576,7 +560,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             s_rs[ph * LT + t] = rowsum;   // read by the epilogue warps after PREADY
             tc_fence_before_sync();
             mbar_arrive(&bars[B_PREADY]);
-            if (t == 0) TRACE(6);
             if (NHALF == 2) {  // C pass for rows [128,256) of C (the K~ warps take rows [0,128))
                 const bool last = (k == NCH - 1);
                 if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
@@ -604,12 +587,9 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             if (k > 0 && !mbar_wait(&bars[B_HFREE], (k - 1) & 1, abort_flag)) break;
             qn_pass<DQK>(smem, s_n, s_qn, gbase + (size_t)k * GW + G_WINQ, warp - 8, lane);
             mbar_arrive(&bars[B_QNDONE]);
-            if (t == 0) TRACE(9);
             scale_rows<DQK>(smem + SM::Q, t, winq);
-            if (t == 0) TRACE(10);
             fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor-core (async) proxy
             mbar_arrive(&bars[B_QSCALED]);
-            if (t == 0) TRACE(11);
         }
     } else if (warp >= 12 && warp < 16) {
         // ================= K~ = K * e^{u_t-x_last} in place; C pass =================
@@ -633,18 +613,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             const bool last = (k == NCH - 1);
             const float decay_next = last ? g[G_SCAL + 2] : g[GW + G_SCAL + 0];
             if (!(mbar_wait(&bars[B_KFULL], ph, abort_flag) && mbar_wait(&bars[B_SDONE], ph, abort_flag))) break;
-            if (r == 0) TRACE(12);
             scale_rows<DQK>(smem + SM::K, r, w);
             fence_proxy_async_smem();
             mbar_arrive(&bars[B_KSCALED]);
-            if (r == 0) TRACE(13);
             // C pass after the state update: refresh Cb (needs the read-out of this tile finished with the
             // old Cb), pre-scale C for the next tile; after the last tile write C out instead.
             if (!(mbar_wait(&bars[B_UPDDONE], ph, abort_flag) && mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
             tc_fence_after_sync();
-            if (r == 0) TRACE(14);
             c_pass_half<DQK>(smem, T_C + lane_off, r, last, decay_next, p.C1 + ((size_t)bh * DQK + r) * p.dv + col0);
-            if (r == 0) TRACE(15);
             if (!last) {
                 tmem_wait_st();
                 fence_proxy_async_smem();
@@ -663,7 +639,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             const bool last = (k == NCH - 1);
             // column sums of K~
             if (!mbar_wait(&bars[B_KSCALED], ph, abort_flag)) break;
-            if (r == 0) TRACE(22);
             const int q = r >> 5, cp = r & 31;   // warp -> 64-column box, lane -> column pair
             float s0 = 0.f, s1 = 0.f;
             if (q < NBOX) {
@@ -681,7 +656,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 s0 = (a0[0] + a0[1]) + (a0[2] + a0[3]);
                 s1 = (a1[0] + a1[1]) + (a1[2] + a1[3]);
             }
-            if (r == 0) TRACE(21);
             mbar_arrive(&bars[B_KREAD]);   // K~ no longer read by the CUDA cores: the tile may be reloaded
             // n is rewritten only after q~ . n of this tile has been taken
             if (!mbar_wait(&bars[B_QNDONE], ph, abort_flag)) break;
@@ -700,7 +674,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             if (!(mbar_wait(&bars[B_PREADY], ph, abort_flag) && mbar_wait(&bars[B_H2DONE], ph, abort_flag) &&
                   mbar_wait(&bars[B_H1DONE], ph, abort_flag))) break;
             tc_fence_after_sync();
-            if (r == 0) TRACE(7);
             const float den = s_qn[r] + s_rs[ph * LT + r];   // q~ . n already carries the row scale
             const float inv = 1.0f / (fmaxf(fabsf(den), g[G_EMT + r]) + p.eps);
             // H -> bf16 h tile staged in the (now idle) V buffer, in the swizzled box layout of the h
@@ -732,7 +705,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
             mbar_arrive(&bars[B_HFREE]);          // H in TMEM has been read
             fence_proxy_async_smem();
             mbar_arrive(&bars[B_HSTAGED]);
-            if (r == 0) TRACE(8);
         }
     }
 
@@ -745,7 +717,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
 
 }  // namespace
 
-bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype) {
+bool mlstm_chunkwise_tc_shape_ok(const ChunkwiseParams &p, int dtype) {
     if (dtype != XLSTM_BF16) return false;
     if (p.dqk != 256 && p.dqk != 128) return false;
     if (p.dv % DVS) return false;
@@ -756,7 +728,13 @@ bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype) {
          reinterpret_cast<uintptr_t>(p.h)) & 15u)
         return false;
     if (p.dv / DVS > 65535) return false;
-    return get_encode_tiled() != nullptr;
+    return true;
+}
+
+bool mlstm_chunkwise_tc_driver_ok() { return get_encode_tiled() != nullptr; }
+
+bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype) {
+    return mlstm_chunkwise_tc_shape_ok(p, dtype) && mlstm_chunkwise_tc_driver_ok();
 }
 
 size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L) {
@@ -840,9 +818,3 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
 }
 
 }  // namespace xl
-
-#ifdef XL_TC_TRACE
-extern "C" int xlstm_debug_trace(long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, xl::g_trace, sizeof(long long) * 64 * 32);
-}
-#endif

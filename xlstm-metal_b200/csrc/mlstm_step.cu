@@ -12,22 +12,11 @@
 
 namespace xl {
 
-// tuning knobs (defaults are the measured best on B200)
-#ifndef XL_STEP_DVT
-#define XL_STEP_DVT 64
-#endif
-#ifndef XL_STEP_THREADS
-#define XL_STEP_THREADS 256
-#endif
-#ifndef XL_STEP_UNROLL
-#define XL_STEP_UNROLL 4
-#endif
-#ifndef XL_STEP_MINB
-#define XL_STEP_MINB 4
-#endif
+// tile shape (the measured best on B200): dv columns per CTA, threads, rows in flight per thread, CTAs per SM
+constexpr int STEP_DVT = 64, STEP_THREADS = 256, STEP_UNROLL = 4, STEP_MIN_CTAS = 4;
 
 template <typename T, int DVT, int THREADS, int UNROLL>
-__global__ void __launch_bounds__(THREADS, XL_STEP_MINB)
+__global__ void __launch_bounds__(THREADS, STEP_MIN_CTAS)
 mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v,
                   const T *__restrict__ ig, const T *__restrict__ fg,
                   const float *C0, const float *__restrict__ n0, const float *__restrict__ m0,
@@ -137,7 +126,7 @@ template <typename T>
 static int mlstm_step_launch(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                              const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
                              float *m1, int BH, int dqk, int dv, float eps, float gate_cap, cudaStream_t st) {
-    constexpr int DVT = XL_STEP_DVT, THREADS = XL_STEP_THREADS, UNROLL = XL_STEP_UNROLL;
+    constexpr int DVT = STEP_DVT, THREADS = STEP_THREADS, UNROLL = STEP_UNROLL;
     dim3 grid(BH, (dv + DVT - 1) / DVT);
     size_t smem = sizeof(float) * (2 * (size_t)dqk + (THREADS / (DVT / 4)) * DVT);
     auto kern = mlstm_step_kernel<T, DVT, THREADS, UNROLL>;
@@ -165,7 +154,7 @@ static int mlstm_step_checked(const void *q, const void *k, const void *v, const
     if (C0 && (n1 == n0 || m1 == m0)) return XLSTM_ERR_INVALID;  // other CTAs of the head still read n0/m0
     if (dv % 4 != 0) return XLSTM_ERR_UNSUPPORTED;
     if (dtype != XLSTM_F32 && dtype != XLSTM_BF16) return XLSTM_ERR_UNSUPPORTED;
-    if ((int64_t)B * NH > 2147483647LL || (dv + XL_STEP_DVT - 1) / XL_STEP_DVT > 65535) return XLSTM_ERR_UNSUPPORTED;
+    if ((int64_t)B * NH > 2147483647LL || (dv + xl::STEP_DVT - 1) / xl::STEP_DVT > 65535) return XLSTM_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == XLSTM_F32)
         return xl::mlstm_step_launch<float>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, gate_cap, st);

@@ -1,17 +1,20 @@
 // Block-diagonal recurrent sLSTM on the tensor cores (bf16, head dim 256): the sequential loop over t
 // with the four recurrent matrices resident in TENSOR MEMORY for the whole sequence.
 //
-// One cluster of 4 CTAs per (head, 32 batch rows); CTA `rank` owns 64 of the head's 256 units, i.e. 256
-// gate-output rows (4 gates x 64 units) of R_g.  Per step the CTA needs pre[m][b] = sum_k R[m][k] h_{t-1}[b][k]
-// for its 256 rows m and 32 batch rows b: two groups of 16 tcgen05.mma (M=128, N=32, K=16) with
+// One cluster of 4 CTAs per (head, NB batch rows), NB = 16 or 32 (16 while all clusters fit on the GPU
+// at once); CTA `rank` owns 64 of the head's 256 units, i.e. 256 gate-output rows (4 gates x 64 units)
+// of R_g.  Per step the CTA needs pre[m][b] = sum_k R[m][k] h_{t-1}[b][k] for its 256 rows m and NB
+// batch rows b: two groups of 16 tcgen05.mma (M=128, N=NB, K=16) with
 //   A = the CTA's slice of R, bf16, written once into TMEM (2 x 128 columns),
-//   B = h_{t-1} [32 x 256] bf16 in shared memory (128-byte swizzle, K-major, 16 KB, double-buffered),
-//   D = fp32 in TMEM (2 x 32 columns).
+//   B = h_{t-1} [NB x 256] bf16 in shared memory (128-byte swizzle, K-major, double-buffered),
+//   D = fp32 in TMEM (2 x NB columns).
 // The accumulators go through shared memory to the threads that own (unit, batch row) cells, which add
-// the input-side pre-activations, run the gating, write h_t to global memory and, as bf16, into the
-// B buffer of the next step in all four CTAs (distributed shared memory); one cluster barrier per
-// step.  Only the MMA's smem traffic is the 1 KB of h per instruction: R is never re-read from
-// shared memory (the CUDA-core version reads its 128 KB slice every step).
+// the input-side pre-activations, run the gating, write h_t to global memory and, as bf16, their box of
+// the next step's B operand.  That box goes to the three peer CTAs by bulk copies from shared memory
+// into distributed shared memory which complete bytes on the RECEIVER's mbarrier, so the loop has no
+// cluster barrier; the MMAs over the CTA's own columns are issued before the wait for the peers' boxes.
+// The MMA's only shared-memory traffic is the h operand: R is never re-read from shared memory (the
+// CUDA-core version reads its 128 KB slice every step).
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -39,13 +42,6 @@ template <int NB> struct TcrCfg {
     static constexpr uint32_t OFF_BAR = OFF_PRE + 4 * TCR_U * PAD * 4;
     static constexpr uint32_t SMEM = OFF_BAR + 64;
 };
-
-#ifdef XL_TCR_TRACE
-__device__ long long g_tcr_trace[64 * 16];
-#define TCR_TRACE(id) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0 && t < 64) g_tcr_trace[t * 16 + (id)] = clock64(); } while (0)
-#else
-#define TCR_TRACE(id) do { } while (0)
-#endif
 
 // gating math on the approximate exp / reciprocal units: absolute error ~1e-6, far below the bf16
 // rounding of the h that is fed back
@@ -190,7 +186,6 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
 
     for (int t = 0; t < S; ++t) {
         const int p = t & 1;
-        TCR_TRACE(0);
         // recurrent pre-activations: pre[m][b] = sum_k R[m][k] h_{t-1}[b][k]
         if (tid == 0 && !*abort_flag) {
             // h_{t-1}: this CTA's own 64 columns were written and fenced last step, so their MMAs go first;
@@ -218,18 +213,15 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
                 mma_commit(bar);
             }
         }
-        TCR_TRACE(1);
         uint32_t graw[4][CPT / 2];
 #pragma unroll
         for (int g = 0; g < 4; ++g)
 #pragma unroll
             for (int w2 = 0; w2 < CPT / 2; ++w2) graw[g][w2] = gnext[g][w2];
         if (t + 1 < S && row_ok) load_gx(t + 1);
-        TCR_TRACE(2);
         if (warp < 8) {
             mbar_wait(bar, (uint32_t)(t & 1), abort_flag);   // bounded; a time-out sets the flag and poisons the state below
             tc_fence_after_sync();
-            TCR_TRACE(3);
             uint32_t v[NB];
             if constexpr (NB == 32) tmem_ld32(T_D + hf * TCR_NB + lane_off, v);
             else tmem_ld16(T_D + hf * TCR_NB + lane_off, v);
@@ -238,9 +230,7 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
             for (int b2 = 0; b2 < TCR_NB; ++b2) sPre[m_row * TCR_PAD + b2] = __uint_as_float(v[b2]);
             tc_fence_before_sync();
         }
-        TCR_TRACE(4);
         __syncthreads();
-        TCR_TRACE(5);
         // gating of the owned cells; h_t to global memory and (bf16) into this CTA's box of the next B buffer
         // the four cells stage by stage (all loads, then all soft-caps, ...): four independent exp /
         // reciprocal chains in flight instead of one after the other
@@ -303,7 +293,6 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
             const __nv_bfloat162 pk = __floats2bfloat162_rn(hv[2 * e2], hv[2 * e2 + 1]);
             hpk[e2] = *reinterpret_cast<const uint32_t *>(&pk);
         }
-        TCR_TRACE(8);
         auto store_h = [&](void *dst) {
             if constexpr (CPT == 4) *reinterpret_cast<uint2 *>(dst) = make_uint2(hpk[0], hpk[CPT / 2 - 1]);
             else *reinterpret_cast<uint32_t *>(dst) = hpk[0];
@@ -313,9 +302,7 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
             unsigned char *mybox = smem + (p ^ 1) * TCR_BBUF + rank * TCR_BBOX;
             store_h(mybox + sw128_off(bb, uq));
             fence_proxy_async_smem();     // generic-proxy writes -> visible to the bulk copies and the MMAs (async proxy)
-            TCR_TRACE(6);
             __syncthreads();
-            TCR_TRACE(7);
             if (tid == 0) {
                 // this CTA's 4 KB box of h_t goes to the same place in the three peers; each copy completes its
                 // bytes on the RECEIVER's barrier.  Own barrier: one arrival + the 3 x 4 KB it will receive.
@@ -379,9 +366,3 @@ int slstm_recurrent_tc(const void *gx, const void *R, const float *rb, const flo
 }
 
 }  // namespace xl
-
-#ifdef XL_TCR_TRACE
-extern "C" int xlstm_debug_trace_slstm(long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, xl::g_tcr_trace, sizeof(long long) * 64 * 16);
-}
-#endif

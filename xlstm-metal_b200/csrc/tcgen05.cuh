@@ -23,33 +23,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-#ifndef XL_TC_WAIT_MODE
-#define XL_TC_WAIT_MODE 0   // 0: try_wait (may suspend), 1: test_wait (pure poll), 2: try_wait with a suspend-time hint
-#endif
-#ifndef XL_TC_WAIT_HINT_NS
-#define XL_TC_WAIT_HINT_NS 32
-#endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
-#if XL_TC_WAIT_MODE == 1
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.b32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-#elif XL_TC_WAIT_MODE == 2
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-        "selp.b32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)XL_TC_WAIT_HINT_NS) : "memory");
-#else
     asm volatile(
         "{\n.reg .pred p;\n"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.b32 %0, 1, 0, p;\n}"
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-#endif
     return ok != 0;
 }
 // Bounded wait.  `abort_flag` (shared memory) lets one timed-out role release all others.

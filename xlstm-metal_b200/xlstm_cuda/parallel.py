@@ -4,8 +4,9 @@ mLSTM heads are independent (no cross-head term in the cell), so a layer shards 
 owns heads ``[r*NH/G, (r+1)*NH/G)`` - its column slices of the q/k/v/gate projections and its
 heads' (C, n, m) - and ONE all-gather of h precedes the replicated out-projection.  Decode batches
 and the sLSTM stack shard by batch with no collective at all.  The backend is NCCL on GPUs and
-gloo in the CPU tests; remote data always lands in local memory through the collective before
-any kernel reads it.
+gloo in the CPU tests.  No kernel ever LOADS from a peer's memory: remote data arrives either
+through the collective or, in the fused head gather, by TMA tile stores that the prefill kernel of
+the owning rank issues into every peer's buffer.
 """
 from __future__ import annotations
 
@@ -74,7 +75,7 @@ class FusedHeadGather:
 
     Every rank owns a ``[B, S, NH, dv]`` buffer in symmetric memory (the layout the out-projection
     GEMM reads, so no permute is needed afterwards).  The chunkwise kernel of rank r writes each h
-    tile of its heads into its own buffer AND, with plain stores over NVLink, into the same slot of
+    tile of its heads into its own buffer AND, by TMA tile stores over NVLink, into the same slot of
     every peer's buffer while the tensor cores work on the next tile; one cross-rank barrier later
     every rank holds all heads.  No NCCL call and no extra pass over h.
     """
