@@ -15,8 +15,11 @@ states (8 layers x 2 buffers = 1 GiB), so every step streams a state that is col
 ``prefill``  chunkwise prefill of BASELINE configs[3] (B=4, S=32768, heads sharded over the
            ranks, NCCL all-gather of h, 4096x4096 out-projection), reported beside the headline.
 At N > 1 the decode batch is sharded (global batch 16*N, no collective): weak scaling.
-``--impl reference`` times the CPU restatement of the reference's torch_native recurrent cell
-(oracle/, OpenMP over batch x heads) on the host cores for the same workload.
+``--impl reference`` times the reference's own torch_native recurrent cell (the unmodified class, placed
+under oracle/_ref by oracle/make_ref.py) on all host cores for the same workload at the same global
+batch; where that file is absent it times the C restatement (oracle/, OpenMP over batch x heads).
+The JSON line stays short: the prefill / sLSTM / soft-cap figures ride inside ``roofline``; the long
+per-kernel tables (glue kernels, 7B-shaped model) go to ``gpurun_out/bench_details.json``.
 """
 from __future__ import annotations
 
@@ -37,6 +40,13 @@ B, NH, DQK, DV = 16, 8, 256, 512
 N_LAYERS = 8          # ring of independent layer states (cold-L2 rule)
 N_INPUT_SETS = 64     # distinct per-step inputs cycled through
 WORKLOAD = "mlstm_decode_step B=16 NH=8 dqk=256 dv=512 bf16 act fp32 state (BASELINE configs[1])"
+
+
+def workload_config(world):
+    """``config`` of the JSON line: the same dict in both arms, so that the two lines describe one workload."""
+    return {"workload": WORKLOAD, "global_batch": B * world, "parallelism": f"batch-sharded x{world}",
+            "l2": f"ring of {N_LAYERS} layer states x 2 buffers = {N_LAYERS * 2 * B * NH * DQK * DV * 4 >> 20} MiB > L2; "
+                  "every step streams a cold state", "state_update": "out-of-place"}
 
 
 def step_bytes(b=B, nh=NH, dqk=DQK, dv=DV, e=2):
@@ -117,66 +127,103 @@ def make_inputs(torch, device, seed):
     return q, k, v, i, f
 
 
-def cpu_baseline(budget_s=15.0, threads=None):
-    """Oracle port of the reference's recurrent cell on the host cores, bounded sample."""
-    import numpy as np
-    from oracle import oracle as xo
-    if threads:
+def host_threads():
+    """Host threads this process may use (under torch.distributed.run OMP_NUM_THREADS is 1: ask the OS)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+class CpuDecode:
+    """The decode workload on the host cores: the reference's own ``mLSTMRecurrentKernelCell`` (bf16 compute,
+    fp32 state; ``kind`` "reference") when oracle/_ref holds it, else the C restatement (``kind`` "port")."""
+
+    def __init__(self, batch, threads, force_port=False):
+        import numpy as np
+        from oracle import make_ref, oracle as xo
+        self.np, self.xo, self.batch, self.threads = np, xo, batch, threads
         xo.set_threads(threads)
-    cores = xo.max_threads()
-    rng = np.random.default_rng(1)
-    q, k = (xo.bf16_round(rng.standard_normal((B, NH, 1, DQK)).astype(np.float32)) for _ in range(2))
-    v = xo.bf16_round(rng.standard_normal((B, NH, 1, DV)).astype(np.float32))
-    i = np.zeros((B, NH, 1), np.float32)
-    f = np.full((B, NH, 1), 3.0, np.float32)
-    st = ((rng.standard_normal((B, NH, DQK, DV)) * 0.1).astype(np.float32),
-          (rng.standard_normal((B, NH, DQK)) * 0.1).astype(np.float32), np.zeros((B, NH), np.float32))
-    xo.mlstm_recurrent(q, k, v, i, f, st)  # warm-up
-    t0 = time.perf_counter()
-    _, st = xo.mlstm_recurrent(q, k, v, i, f, st)
-    one = time.perf_counter() - t0
-    n = int(max(3, min(2000, budget_s / max(one, 1e-6))))
-    t0 = time.perf_counter()
-    for _ in range(n):
-        _, st = xo.mlstm_recurrent(q, k, v, i, f, st)
-    dt = time.perf_counter() - t0
-    return {"value": B * n / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": f"{n} decode steps of the headline workload, {dt:.1f} s, oracle C port (OpenMP over batch x heads)"}
+        cls = None if force_port else make_ref.load_cell_class()
+        self.kind = "reference" if cls is not None else "port"
+        rng = np.random.default_rng(1)
+        n_sets = 8
+        q, k = (xo.bf16_round(rng.standard_normal((n_sets, batch, NH, 1, DQK)).astype(np.float32)) for _ in range(2))
+        v = xo.bf16_round(rng.standard_normal((n_sets, batch, NH, 1, DV)).astype(np.float32))
+        i = xo.bf16_round((15 * np.tanh(rng.standard_normal((n_sets, batch, NH, 1)) / 15)).astype(np.float32))
+        f = xo.bf16_round((15 * np.tanh((rng.standard_normal((n_sets, batch, NH, 1)) + 3) / 15)).astype(np.float32))
+        st = ((rng.standard_normal((batch, NH, DQK, DV)) * 0.1).astype(np.float32),
+              (rng.standard_normal((batch, NH, DQK)) * 0.1).astype(np.float32), np.zeros((batch, NH), np.float32))
+        self.n_sets = n_sets
+        if cls is not None:
+            import torch
+            torch.set_num_threads(threads)
+            self.torch = torch
+            self.cell = cls(NH, DQK, DV, compute_dtype=torch.bfloat16, state_dtype=torch.float32)
+            self.inputs = [tuple(torch.from_numpy(a[s_]).to(torch.bfloat16) for a in (q, k, v, i, f)) for s_ in range(n_sets)]
+            self.state = tuple(torch.from_numpy(a) for a in st)
+            self.what = "reference torch_native mLSTMRecurrentKernelCell (bf16 compute, fp32 state), torch CPU"
+        else:
+            self.inputs = [tuple(a[s_] for a in (q, k, v, i, f)) for s_ in range(n_sets)]
+            self.state = st
+            self.what = "oracle C port of the torch_native recurrent cell (OpenMP over batch x heads)"
+
+    def step(self, t):
+        a = self.inputs[t % self.n_sets]
+        if self.kind == "reference":
+            with self.torch.no_grad():
+                _, self.state = self.cell(*a, self.state)
+        else:
+            _, self.state = self.xo.mlstm_recurrent(*a, self.state)
+
+    def run(self, steps, warmup, budget_s):
+        """Up to ``steps`` decode steps within ``budget_s`` seconds; returns (steps done, seconds)."""
+        for t in range(warmup):
+            self.step(t)
+        t0 = time.perf_counter()
+        done = 0
+        while done < steps:
+            self.step(done)
+            done += 1
+            if time.perf_counter() - t0 > budget_s and done >= 3:
+                break
+        return done, time.perf_counter() - t0
+
+
+def cpu_baseline(budget_s=12.0):
+    """The decode workload on the host cores beside the GPU number, bounded sample (rank 0, N=1)."""
+    threads = host_threads()
+    ref = CpuDecode(B, threads)
+    n, dt = ref.run(2000, 1, budget_s)
+    out = {"value": B * n / dt, "unit": "tokens/s", "cores": threads, "kind": ref.kind,
+           "sample": f"{n} decode steps of the headline workload in {dt:.1f} s, {ref.what}"}
+    if ref.kind == "reference":     # the C restatement beside it, for scale
+        port = CpuDecode(B, threads, force_port=True)
+        n2, dt2 = port.run(2000, 1, 5.0)
+        out["port_value"] = B * n2 / dt2
+    return out
 
 
 def run_reference(args):
-    """CPU arm: the restated reference cell, all host threads, same workload and metric."""
+    """CPU arm: the reference's cell on all host threads, same workload, metric and global batch as our arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import numpy as np
-    from oracle import oracle as xo
-    cores = xo.max_threads()
-    rng = np.random.default_rng(1)
-    q, k = (xo.bf16_round(rng.standard_normal((N_INPUT_SETS, B, NH, 1, DQK)).astype(np.float32)) for _ in range(2))
-    v = xo.bf16_round(rng.standard_normal((N_INPUT_SETS, B, NH, 1, DV)).astype(np.float32))
-    i = xo.bf16_round((15 * np.tanh(rng.standard_normal((N_INPUT_SETS, B, NH, 1)) / 15)).astype(np.float32))
-    f = xo.bf16_round((15 * np.tanh((rng.standard_normal((N_INPUT_SETS, B, NH, 1)) + 3) / 15)).astype(np.float32))
-    st = ((rng.standard_normal((B, NH, DQK, DV)) * 0.1).astype(np.float32),
-          (rng.standard_normal((B, NH, DQK)) * 0.1).astype(np.float32), np.zeros((B, NH), np.float32))
-    # a CPU step costs ~10-40 ms, so cap the count to keep the arm within a few minutes
-    steps = min(args.steps, 2000)
-    warm = min(args.warmup, 20)
-    for t in range(warm):
-        s = t % N_INPUT_SETS
-        _, st = xo.mlstm_recurrent(q[s], k[s], v[s], i[s], f[s], st)
-    t0 = time.perf_counter()
-    for t in range(steps):
-        s = t % N_INPUT_SETS
-        _, st = xo.mlstm_recurrent(q[s], k[s], v[s], i[s], f[s], st)
-    dt = time.perf_counter() - t0
-    val = B * steps / dt
+    world = max(1, args.gpus)
+    batch = B * world
+    threads = host_threads()
+    ref = CpuDecode(batch, threads)
+    # a CPU step costs tens of milliseconds, so the run is bounded in time as well as in steps
+    warm = min(args.warmup, 3)
+    steps, dt = ref.run(min(args.steps, 2000), warm, 60.0)
+    val = batch * steps / dt
     line = {"impl": "reference", "metric": "mlstm_decode_tokens_per_s", "value": val, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": dt / steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": WORKLOAD},
-            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
-                             "sample": f"{steps} full decode steps, oracle C port of the torch_native recurrent cell"},
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if ref.kind == "reference" else "f32",
+            "data": "synthetic", "config": workload_config(world),
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": ref.kind,
+                             "sample": f"{steps} full decode steps at global batch {batch} in {dt:.1f} s, {ref.what}"},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -337,33 +384,57 @@ def run_ours(args):
 
     hbm, tf, which = peaks()
     achieved = step_bytes() / (ms / K * 1e-3) / 1e9  # this rank's kernel
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                "traffic": TRAFFIC_PER_LAUNCH, "kernel": "mlstm_step_kernel", "peak_source": which,
+                "algorithmic_bytes_per_launch": step_bytes()}
+    details = {}
+    if prefill is not None:
+        # the prefill half of the metric, kept inside `roofline` so that it survives in the run records
+        r = prefill["roofline"]
+        roofline["prefill"] = {
+            "frac": r["frac"], "tflops": r["achieved"], "peak_tflops": r["peak"], "hbm_frac": r["hbm_frac"],
+            "cell_ms": prefill["cell_ms"], "tokens_per_s": prefill["cell_tokens_per_s"],
+            "with_allgather_outproj_ms": prefill["with_allgather_outproj_ms"],
+            "nccl_variant_ms": prefill["nccl_allgather_variant_ms"], "world": world,
+            "gather_check": prefill["gather_check"], "gather_gbs_per_rank": prefill["gather_gbs_per_rank"],
+            "token_sharded_outproj_ms": prefill["token_sharded_outproj_ms"], "token_sharded_check": prefill["token_sharded_check"],
+            "workload": f"B=4 S={args.prefill_seq} NH=8 256/512 bf16 (BASELINE configs[3]), heads x{world}",
+            "kernel": "mlstm_chunkwise_tc_fast_kernel", "bound": "tensor"}
+        details["prefill"] = prefill
+    launches = K
+    if not args.no_extras:
+        sl = run_slstm(torch, dist, device, world, rank)
+        details["slstm"] = sl
+        roofline["slstm_ms"] = sl["ms"]
+        if rank == 0:
+            sc = run_softcap(torch, ops, device)
+            details["softcap"] = sc
+            roofline["softcap_frac"] = sc["roofline"]["frac"]
+            details["glue"] = run_glue(torch, ops, device)
+            roofline["glue_frac"] = {k_: round(v_["roofline"]["frac"], 3) for k_, v_ in details["glue"].items()}
+            if not args.no_model:
+                mo = run_model(torch, device, 2048, 256)
+                details["model"] = mo
+                roofline["model_7b"] = {"prefill_tokens_per_s": mo["prefill_tokens_per_s"],
+                                        "decode_tokens_per_s": mo["decode_tokens_per_s"]}
     line = {
         "metric": "mlstm_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": B * world, "parallelism": f"batch-sharded x{world}",
-                   "l2": f"ring of {N_LAYERS} layer states x 2 buffers = {N_LAYERS * 2 * B * NH * DQK * DV * 4 >> 20} MiB > L2; "
-                         "every step streams a cold state", "state_update": "out-of-place", "launch": "CUDA graph replay of the step loop"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                     "traffic": TRAFFIC_PER_LAUNCH, "kernel": "mlstm_step_kernel", "peak_source": which,
-                     "algorithmic_bytes_per_launch": step_bytes()},
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(world), "roofline": roofline,
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / K},
-        "gpu_launches": K,
+        "gpu_launches": launches, "launch": "CUDA graph replay of the step loop",
         "clocks": clk.summary(),
     }
-    if prefill is not None:
-        line["prefill"] = prefill
-    if not args.no_extras:
-        line["slstm"] = run_slstm(torch, dist, device, world, rank)
-        if rank == 0:
-            line["softcap"] = run_softcap(torch, ops, device)
-            line["glue"] = run_glue(torch, ops, device)
-            if not args.no_model:
-                line["model"] = run_model(torch, device, 2048, 256)
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
         print(json.dumps(line), flush=True)
+        try:    # the long per-kernel tables: a file beside the run, not part of the line
+            out = ROOT / "gpurun_out"
+            out.mkdir(exist_ok=True)
+            (out / f"bench_details_n{world}.json").write_text(json.dumps({"line": line, "details": details}, indent=1))
+        except OSError:
+            pass
     if world > 1:
         dist.destroy_process_group()
 
@@ -407,7 +478,17 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
     e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     one()
     torch.cuda.synchronize()
+    gather_check = None
     if world > 1:
+        dist.barrier()
+    if fused is not None:
+        # the fused gather must leave, on every rank, exactly what a separate all-gather of h leaves
+        h_loc, _ = ops.mlstm_chunkwise(q, k, v, i, f, None, L, 1e-6, ws)
+        want = all_gather_heads(h_loc).permute(0, 2, 1, 3).reshape(Bp, Sp, NH * DV)
+        same = torch.tensor([1 if torch.equal(fused.buf.view(Bp, Sp, NH * DV), want) else 0], device=device)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        gather_check = "bit-exact" if int(same.item()) == 1 else "MISMATCH"
+        del h_loc, want
         dist.barrier()
     reps = args.prefill_reps
     e[0].record()
@@ -428,20 +509,31 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
         torch.cuda.synchronize()
         dist.barrier()
         nccl_ms = _time_cuda(torch, one_nccl, reps)
-    t_cell = torch.tensor([e[0].elapsed_time(e[1]) / reps, e[2].elapsed_time(e[3]) / reps, nccl_ms], device=device)
+    # the cell with the fused gather alone (no out-projection): the stores to the peers ride inside the kernel
+    gat_ms = 0.0
+    if fused is not None:
+        dist.barrier()
+        gat_ms = _time_cuda(torch, lambda: fused.run(q, k, v, i, f, None, out_proj=None, workspace=ws), reps)
+    tok_ms, tok_check = None, None
+    t_cell = torch.tensor([e[0].elapsed_time(e[1]) / reps, e[2].elapsed_time(e[3]) / reps, nccl_ms, gat_ms], device=device)
     if world > 1:
         dist.all_reduce(t_cell, op=dist.ReduceOp.MAX)
-    cell_ms, full_ms, nccl_ms = (float(x) for x in t_cell)
+    cell_ms, full_ms, nccl_ms, cell_ms_gather = (float(x) for x in t_cell)
     tokens = Bp * Sp
     flop = tokens * NH * (4 * DQK * DV + L * (DQK + DV))      # whole job, causal-half count
     byts = tokens * NH * ((2 * DQK + 2 * DV) * 2 + 2 * 2)
     hbm, tf, which = peaks()
+    # bytes of h every rank pushes to its peers during the cell (fused gather), over the cell time
+    gather_gbs = (world - 1) * Bp * Sp * nh_local * DV * 2 / (cell_ms_gather * 1e-3) / 1e9 if fused is not None else None
     return {"workload": f"mlstm_chunkwise_prefill B={Bp} S={Sp} NH={NH} dqk={DQK} dv={DV} L={L} bf16 (BASELINE configs[3])",
             "parallelism": f"heads sharded x{world}, fused all-gather of h, replicated out-proj", "scaling": "strong",
             "cell_tokens_per_s": tokens / (cell_ms * 1e-3), "cell_ms": cell_ms,
             "with_allgather_outproj_tokens_per_s": tokens / (full_ms * 1e-3), "with_allgather_outproj_ms": full_ms,
             "gather": ("fused: kernel epilogue stores h into every rank's buffer over NVLink" if world > 1 else "single rank"),
+            "gather_check": gather_check, "gather_gbs_per_rank": gather_gbs, "cell_with_gather_ms": cell_ms_gather,
+            "nvlink_peak_gbs_per_direction": 900.0,
             "nccl_allgather_variant_ms": (nccl_ms if world > 1 else None),
+            "token_sharded_outproj_ms": tok_ms, "token_sharded_check": tok_check,
             "roofline": {"bound": "tensor", "achieved": flop / world / (cell_ms * 1e-3) / 1e12, "peak": tf,
                          "unit": "TFLOP/s", "frac": flop / world / (cell_ms * 1e-3) / 1e12 / tf,
                          "hbm_achieved_gbs": byts / world / (cell_ms * 1e-3) / 1e9, "hbm_frac": byts / world / (cell_ms * 1e-3) / 1e9 / hbm,

@@ -98,6 +98,16 @@ int xlstm_mlstm_chunkwise_fwd(const void *q, const void *k, const void *v, const
 size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int dv, int L, int dtype);
 
 /*
+ * The bf16 tensor-core forward has two kernels and picks one per (batch, head) on the device: one for gates
+ * whose running maximum rises by at most e^30 within any 128-token tile (every gate factor is then applied
+ * to the V rows and to the output rows, none to the Q and K tiles), and a general one whose exponents are all
+ * differences <= 0 and which therefore takes any gate pattern.  Both compute the same function.
+ * on != 0 sends every head to the general kernel (process-wide; meant for tests and comparisons),
+ * on == 0 restores the per-head choice.  No counterpart in the reference.
+ */
+int xlstm_mlstm_chunkwise_set_general_only(int on);
+
+/*
  * xlstm_mlstm_chunkwise_fwd fused with the all-gather of h for head-sharded execution: the
  * epilogue stores every h tile to `h` AND, with the same strides and offsets, to `n_peers` (<= 7)
  * further base pointers - the same head slot of the peer GPUs' [B,S,NH_total,dv] buffers, mapped
@@ -134,6 +144,17 @@ int xlstm_mlstm_chunkwise_fwd_static(const void *q, const void *k, const void *v
                                      const int64_t *strides, void *stream);
 
 /*
+ * Outcome of the device-side waits of the last chunkwise forward that used `workspace` (NULL = the built-in
+ * block of xlstm_mlstm_chunkwise_fwd_static): the tensor-core kernels bound every wait on a barrier; a wait
+ * that gives up sets a status word in the scratch, releases the other roles of its CTA and the kernel ends
+ * normally with incomplete results.  This call copies that word back (it SYNCHRONISES `stream`) and returns
+ * XLSTM_OK or XLSTM_ERR_TIMEOUT.  The forward calls themselves never synchronise, so a caller that wants the
+ * check makes this call where it synchronises anyway.  No counterpart in the reference (its launchers block
+ * on waitUntilCompleted and have no device-side waits).
+ */
+int xlstm_mlstm_chunkwise_status(const void *workspace, void *stream);
+
+/*
  * Packaged sLSTM cell (scalar gates per head, state c,n,m) applied to S
  * timesteps in one launch:
  *   m' = max(m + logsigmoid(f), i); c' = e^{m+logsig(f)-m'} c + e^{i-m'} tanh(z);
@@ -167,6 +188,13 @@ int xlstm_slstm_recurrent(const void *gx, const void *R, const float *rb,
                           const float *c0, const float *n0, const float *h0, const float *m0,
                           void *hs, float *c1, float *n1, float *h1, float *m1,
                           int B, int S, int NH, int dh, float cap, int dtype, void *stream);
+
+/*
+ * The same for the tensor-core path of xlstm_slstm_recurrent (its CTAs wait, bounded, for their cluster
+ * peers' slices of h_t): XLSTM_ERR_TIMEOUT if any launch on this device since the last query gave up a wait
+ * (its final state m is then NaN as well); the word is cleared by the query.  Synchronises `stream`.
+ */
+int xlstm_slstm_recurrent_status(void *stream);
 
 /*
  * Gate soft-cap folded into the consumers: the same two functions with the raw gate projections as

@@ -30,5 +30,9 @@ bool mlstm_chunkwise_tc_driver_ok();
 bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype);
 size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L);
 int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspace_bytes, cudaStream_t st);
+// 1: every head takes the general tensor-core kernel whatever its gates are; 0: per-head choice (default)
+void mlstm_chunkwise_tc_set_general_only(int on);
+
+int mlstm_chunkwise_static_scratch(void **out);
 
 }  // namespace xl

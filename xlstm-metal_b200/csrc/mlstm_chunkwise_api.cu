@@ -16,6 +16,27 @@ void dense_strides(xl::ChunkwiseParams &p) {
 
 }  // namespace
 
+extern "C" int xlstm_mlstm_chunkwise_set_general_only(int on) {
+    xl::mlstm_chunkwise_tc_set_general_only(on);
+    return XLSTM_OK;
+}
+
+extern "C" int xlstm_mlstm_chunkwise_status(const void *workspace, void *stream) {
+    const void *ws = workspace;
+    if (!ws) {
+        void *blk = nullptr;
+        const int rc = xl::mlstm_chunkwise_static_scratch(&blk);
+        if (rc != XLSTM_OK) return rc;
+        ws = blk;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int word = 0;   // the status word is the first int of the scratch
+    if (cudaMemcpyAsync(&word, ws, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+        return XLSTM_ERR_CUDA;
+    return word ? XLSTM_ERR_TIMEOUT : XLSTM_OK;
+}
+
 extern "C" size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int dv, int L, int dtype) {
     if (dtype != XLSTM_BF16) return 0;
     return xl::mlstm_chunkwise_tc_workspace(B, NH, S, dqk, dv, L);

@@ -47,6 +47,11 @@ int scratch_for_current_device(void **out) {
 
 }  // namespace
 
+namespace xl {
+// device address of the built-in scratch block on the current device (for the status query)
+int mlstm_chunkwise_static_scratch(void **out) { return scratch_for_current_device(out); }
+}  // namespace xl
+
 extern "C" int xlstm_mlstm_chunkwise_fwd_static(const void *q, const void *k, const void *v, const void *ig,
                                                 const void *fg, const float *C0, const float *n0, const float *m0,
                                                 void *h, float *C1, float *n1, float *m1, int B, int NH, int S,

@@ -30,45 +30,35 @@
 // TMEM columns: C [0,256)  S/P [256,384)  H [384,512).
 // Every mbarrier wait is bounded; a time-out sets the status word in the
 // scratch buffer, releases all roles and frees TMEM before the CTA returns.
-#include "mlstm_chunkwise.cuh"
-#include "tcgen05.cuh"
+#include <atomic>
+
+#include "mlstm_chunkwise_tc.cuh"
 
 namespace xl {
 
 namespace {
 
 using namespace tc;
-
-constexpr int LT = 128;        // tokens per tile
-constexpr int DVS = 128;       // dv columns per CTA
-constexpr int THREADS = 640;
-constexpr int GW = 6 * LT;     // floats of gate scratch per (head, tile)
-constexpr int G_U2 = 0, G_X2 = LT, G_WINQ = 2 * LT, G_W = 3 * LT, G_EMT = 4 * LT, G_SCAL = 5 * LT;
-constexpr float LOG2E = 1.4426950408889634f;
-constexpr size_t WS_HEADER = 256;  // status word lives in the first bytes of the scratch
-
-struct TcParams {
-    CUtensorMap tq, tk, tv;
-    const float *gates;            // [B*NH][NCH][GW]
-    const float *C0, *n0;
-    CUtensorMap th[8];             // h of this GPU, then the same head slot of up to 7 peer GPUs' buffers
-    int n_h;                       // number of destinations (1 + peers)
-    float *C1, *n1;
-    int NH, dv, NCH;
-    float eps, log2_qscale;
-    int *status;
-};
+using namespace tcw;
 
 // ---------------------------------------------------------------------------
-// gate pre-pass: one CTA per (batch, head).  Only the stabiliser m couples the tiles, and
-// only through two numbers per tile (G = sum of log-sigmoid f, U = max of u = i - b), so:
-//   phase 1  all warps, tiles in parallel: G_c, U_c              -> shared memory
-//   phase 2  one thread: m_{c+1} = G_c + max(m_c, U_c)           (NCH scalar steps)
-//   phase 3  all warps, tiles in parallel: the per-token scalars -> scratch
+// gate pre-pass.  Only the stabiliser m couples the tiles, and only through two numbers per tile
+// (G = sum of log-sigmoid f, U = max of u = i - b), so it runs as three small launches:
+//   mlstm_gate_stats_kernel   one warp per (head, tile): G_c, U_c                      -> scratch
+//   mlstm_gate_chain_kernel   one warp per head: m_{c+1} = G_c + max(m_c, U_c), the frame rho of the
+//                             lazily rescaled accumulator, the head's path flag        -> scratch
+//   mlstm_gate_write_kernel   one warp per (head, tile): the per-token scalars          -> scratch
 // Sums and maxima are kept in double so that differences of large cumulative sums stay exact.
 // ---------------------------------------------------------------------------
-constexpr int GP_THREADS = 256;
-constexpr double RESCALE_AT = 30.0;   // rescale C~ when the frame exponent would exceed e^30
+constexpr int GP_THREADS = 256;        // 8 warps = 8 tiles per CTA
+constexpr int GC = 6;                  // doubles of chain scratch per (head, tile): G, U, m_in, rho_in, rho_out, mul
+constexpr double RESCALE_AT = 30.0;    // general kernel: rescale C~ when the frame exponent would exceed e^30
+// A head takes the bounded-spread kernel when no tile raises the running maximum by more than SPREAD_LIMIT (in
+// natural-log units): its per-token factors a_s = e^{u_s - m - rho} then stay below e^{SPREAD_LIMIT + RESCALE_AT_B}
+// = e^65, which leaves the fp32 accumulators (sums of a few thousand products of a_s with O(10) values) a
+// margin of e^10 below overflow.
+constexpr double SPREAD_LIMIT = 45.0;
+constexpr double RESCALE_AT_B = 20.0;
 
 template <typename T>
 __device__ __forceinline__ void gate_tile_scan(const T *ip, const T *fp, int64_t sg_s, float cap, int c, int lane,
@@ -112,219 +102,123 @@ __device__ __forceinline__ void gate_tile_scan(const T *ip, const T *fp, int64_t
 
 template <typename T>
 __global__ void __launch_bounds__(GP_THREADS)
-mlstm_gate_prep_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64_t sg_b, int64_t sg_h, int64_t sg_s,
-                       const float *__restrict__ m0, float *__restrict__ gates, float *__restrict__ m_out, int NH,
-                       int NCH, float qscale, float cap) {
-    extern __shared__ double s_gp[];   // [NCH] each: G, U (-> m before the tile), rho before the tile, C multiplier
-    double *sG = s_gp, *sU = s_gp + NCH, *sRho = s_gp + 2 * NCH, *sMul = s_gp + 3 * NCH;
-    const int bh = blockIdx.x, b = bh / NH, hd = bh % NH;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = GP_THREADS / 32;
-    const T *ip = ig + b * sg_b + hd * sg_h;
-    const T *fp = fg + b * sg_b + hd * sg_h;
+mlstm_gate_stats_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64_t sg_b, int64_t sg_h, int64_t sg_s,
+                        double *__restrict__ chain, int NH, int NCH, float cap) {
+    const int bh = blockIdx.y, b = bh / NH, hd = bh % NH;
+    const int lane = threadIdx.x & 31, c = blockIdx.x * (GP_THREADS / 32) + (threadIdx.x >> 5);
+    if (c >= NCH) return;
     double bcum[4], u[4], pmax[4], excl, G, U;
-    for (int c = warp; c < NCH; c += nwarp) {
-        gate_tile_scan<T>(ip, fp, sg_s, cap, c, lane, bcum, u, pmax, excl, G, U);
-        if (lane == 0) { sG[c] = G; sU[c] = U; }
+    gate_tile_scan<T>(ig + b * sg_b + hd * sg_h, fg + b * sg_b + hd * sg_h, sg_s, cap, c, lane, bcum, u, pmax, excl, G, U);
+    if (lane == 0) {
+        double *o = chain + ((size_t)bh * NCH + c) * GC;
+        o[0] = G; o[1] = U;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        // C is kept in TMEM as C~ = C e^{-rho}: rho absorbs the per-tile decay so that the accumulator is
-        // NOT rescaled every tile; only when -rho would exceed RESCALE_AT is C~ multiplied once (sMul).
-        double m = m0 ? (double)m0[bh] : 0.0, rho = 0.0;
-        for (int c = 0; c < NCH; ++c) {
-            const double x_last = fmax(m, sU[c]);
-            const double logdec = m - x_last;           // log of the decay applied to the carried state, <= 0
-            sRho[c] = rho;
-            if (rho + logdec < -RESCALE_AT) { sMul[c] = exp(rho + logdec); rho = 0.0; }
-            else { sMul[c] = 1.0; rho += logdec; }
-            const double mn = sG[c] + x_last;
-            sU[c] = m;   // stabiliser carried INTO tile c
-            sG[c] = rho; // frame of the state AFTER tile c's update (G itself is recomputed in phase 3)
-            m = mn;
+}
+
+// One warp per head.  The chain is sequential but tiny; the warp loads 32 tiles' (G, U) at once and every lane
+// walks them through shuffles, keeping the results of "its" tile for a coalesced write.
+__global__ void __launch_bounds__(32)
+mlstm_gate_chain_kernel(const float *__restrict__ m0, double *__restrict__ chain, float *__restrict__ m_out,
+                        int *__restrict__ path, int NCH, int general_only) {
+    const int bh = blockIdx.x, lane = threadIdx.x;
+    double *ch = chain + (size_t)bh * NCH * GC;
+    // pass 1: the stabiliser chain, and whether every tile's spread x_last - m is bounded
+    double m = m0 ? (double)m0[bh] : 0.0;
+    bool bounded = !general_only;
+    for (int c0 = 0; c0 < NCH; c0 += 32) {
+        const int c = c0 + lane;
+        const double Gl = c < NCH ? ch[(size_t)c * GC + 0] : 0.0, Ul = c < NCH ? ch[(size_t)c * GC + 1] : 0.0;
+        double m_mine = 0.0;
+        const int nb = min(32, NCH - c0);
+        for (int j = 0; j < nb; ++j) {
+            const double Gj = __shfl_sync(0xffffffffu, Gl, j), Uj = __shfl_sync(0xffffffffu, Ul, j);
+            const double x_last = fmax(m, Uj);
+            if (x_last - m > SPREAD_LIMIT) bounded = false;
+            if (j == lane) m_mine = m;
+            m = Gj + x_last;
         }
-        m_out[bh] = (float)m;
+        if (c < NCH) ch[(size_t)c * GC + 2] = m_mine;    // stabiliser carried INTO tile c
     }
-    __syncthreads();
-    for (int c = warp; c < NCH; c += nwarp) {
-        gate_tile_scan<T>(ip, fp, sg_s, cap, c, lane, bcum, u, pmax, excl, G, U);
-        const double m = sU[c], rho_in = sRho[c], rho_out = sG[c];
-        const double x_last = fmax(U, m);
-        const double carry = fmax(excl, m);
-        float *g = gates + ((size_t)bh * NCH + c) * GW;
-        float4 o_u2, o_x2, o_wq, o_w, o_em;
-        float *pu = &o_u2.x, *px = &o_x2.x, *pq = &o_wq.x, *pw = &o_w.x, *pe = &o_em.x;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const double xt = fmax(pmax[e], carry);
-            pu[e] = (float)(u[e] * (double)LOG2E);
-            px[e] = (float)(xt * (double)LOG2E);
-            pq[e] = expf((float)(m - xt + rho_in)) * qscale;   // read-out sees C~ = C e^{-rho_in}
-            pw[e] = expf((float)(u[e] - x_last - rho_out));     // new tokens enter the frame after the update
-            pe[e] = expf(-(float)(bcum[e] + xt));
+    if (lane == 0) { m_out[bh] = (float)m; path[bh] = bounded ? 1 : 0; }
+    // pass 2: C is kept in TMEM as C~ = C e^{-rho}: rho absorbs the per-tile decay so that the accumulator is
+    // NOT rescaled every tile; only when -rho would exceed RESCALE_AT is C~ multiplied once (mul).
+    // General kernel: the multiplication happens BEFORE tile c's update (mul also carries the decay of that
+    // tile); bounded-spread kernel: AFTER tile c's update, so that update and read-out of a tile share one
+    // frame.  rho_in = frame the read-out of tile c sees, rho_out = frame after tile c's update.
+    double rho = 0.0;
+    for (int c0 = 0; c0 < NCH; c0 += 32) {
+        const int c = c0 + lane;
+        double ld = 0.0;
+        if (c < NCH) ld = ch[(size_t)c * GC + 2] - fmax(ch[(size_t)c * GC + 2], ch[(size_t)c * GC + 1]);   // m - x_last <= 0
+        double rin = 0.0, rout = 0.0, mul = 1.0;
+        const int nb = min(32, NCH - c0);
+        for (int j = 0; j < nb; ++j) {
+            const double logdec = __shfl_sync(0xffffffffu, ld, j);
+            const double r_in = rho;
+            double r_out, mu = 1.0;
+            if (bounded) {
+                rho += logdec;
+                r_out = rho;
+                if (rho < -RESCALE_AT_B) { mu = exp(rho); rho = 0.0; }
+            } else {
+                if (rho + logdec < -RESCALE_AT) { mu = exp(rho + logdec); rho = 0.0; }
+                else rho += logdec;
+                r_out = rho;
+            }
+            if (j == lane) { rin = r_in; rout = r_out; mul = mu; }
         }
-        *reinterpret_cast<float4 *>(g + G_U2 + lane * 4) = o_u2;
-        *reinterpret_cast<float4 *>(g + G_X2 + lane * 4) = o_x2;
-        *reinterpret_cast<float4 *>(g + G_WINQ + lane * 4) = o_wq;
-        *reinterpret_cast<float4 *>(g + G_W + lane * 4) = o_w;
-        *reinterpret_cast<float4 *>(g + G_EMT + lane * 4) = o_em;
-        if (lane == 0) {
-            g[G_SCAL + 0] = (float)sMul[c];             // multiplier for C~ and n~ before this tile (1 = leave alone)
-            g[G_SCAL + 1] = (float)(G + x_last);        // stabiliser after this tile
-            g[G_SCAL + 2] = expf((float)rho_out);       // C = C~ * this after the tile (used for the final state)
+        if (c < NCH) {
+            ch[(size_t)c * GC + 3] = rin; ch[(size_t)c * GC + 4] = rout; ch[(size_t)c * GC + 5] = mul;
         }
     }
 }
 
-// ---------------------------------------------------------------------------
-// main kernel
-// ---------------------------------------------------------------------------
-template <int DQK> struct Smem {
-    static constexpr int NBOX = DQK / 64;                  // 64-column TMA boxes of a Q / K tile
-    static constexpr uint32_t BOX = LT * 128;              // bytes of one box: 128 rows x 128 B
-    static constexpr uint32_t Q = 0;
-    static constexpr uint32_t K = Q + NBOX * BOX;
-    static constexpr uint32_t V = K + NBOX * BOX;          // 2 boxes (128 dv columns)
-    static constexpr uint32_t CB = V + 2 * BOX;            // 2 N-blocks of [DQK rows x 128 B]
-    static constexpr uint32_t CB_BLOCK = DQK * 128;
-    static constexpr uint32_t SMALL = CB + 2 * CB_BLOCK;
-    static constexpr uint32_t N_VEC = SMALL;               // float[DQK]   normaliser n
-    static constexpr uint32_t QN = N_VEC + DQK * 4;        // float[LT]    q . n of the current tile
-    static constexpr uint32_t INV = QN + LT * 4;           // float[2][LT] row sums of P, by tile parity
-    static constexpr uint32_t BARS = INV + 2 * LT * 4;     // uint64[24]
-    static constexpr uint32_t MISC = BARS + 24 * 8;        // tmem base, abort flag
-    static constexpr uint32_t TOTAL = MISC + 16;
-};
+template <typename T>
+__global__ void __launch_bounds__(GP_THREADS)
+mlstm_gate_write_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64_t sg_b, int64_t sg_h, int64_t sg_s,
+                        const double *__restrict__ chain, const int *__restrict__ path, float *__restrict__ gates,
+                        int NH, int NCH, float qscale, float cap) {
+    const int bh = blockIdx.y, b = bh / NH, hd = bh % NH;
+    const int lane = threadIdx.x & 31, c = blockIdx.x * (GP_THREADS / 32) + (threadIdx.x >> 5);
+    if (c >= NCH) return;
+    const bool bounded = path[bh] != 0;
+    double bcum[4], u[4], pmax[4], excl, G, U;
+    gate_tile_scan<T>(ig + b * sg_b + hd * sg_h, fg + b * sg_b + hd * sg_h, sg_s, cap, c, lane, bcum, u, pmax, excl, G, U);
+    const double *ch = chain + ((size_t)bh * NCH + c) * GC;
+    const double m = ch[2], rho_in = ch[3], rho_out = ch[4];
+    const double x_last = fmax(U, m);
+    const double carry = fmax(excl, m);
+    float *g = gates + ((size_t)bh * NCH + c) * GW;
+    float4 o_u2, o_x2, o_wq, o_w, o_em;
+    float *pu = &o_u2.x, *px = &o_x2.x, *pq = &o_wq.x, *pw = &o_w.x, *pe = &o_em.x;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const double xt = fmax(pmax[e], carry);
+        pu[e] = (float)(u[e] * (double)LOG2E);
+        px[e] = (float)(xt * (double)LOG2E);
+        pq[e] = expf((float)(m - xt + rho_in)) * qscale;   // read-out sees C~ = C e^{-rho_in}
+        // weight of token s in the update: general kernel e^{u_s - x_last - rho_out} (<= e^{RESCALE_AT});
+        // bounded-spread kernel a_s = e^{u_s - m - rho_in} (the same number except on rescale tiles)
+        pw[e] = bounded ? expf((float)(u[e] - m - rho_in)) : expf((float)(u[e] - x_last - rho_out));
+        pe[e] = expf(-(float)(bcum[e] + xt));
+    }
+    *reinterpret_cast<float4 *>(g + G_U2 + lane * 4) = o_u2;
+    *reinterpret_cast<float4 *>(g + G_X2 + lane * 4) = o_x2;
+    *reinterpret_cast<float4 *>(g + G_WINQ + lane * 4) = o_wq;
+    *reinterpret_cast<float4 *>(g + G_W + lane * 4) = o_w;
+    *reinterpret_cast<float4 *>(g + G_EMT + lane * 4) = o_em;
+    if (lane == 0) {
+        g[G_SCAL + 0] = (float)ch[5];               // multiplier for C~ and n~: before this tile (general) / after its update (bounded)
+        g[G_SCAL + 1] = (float)(G + x_last);        // stabiliser after this tile
+        g[G_SCAL + 2] = expf((float)rho_out);       // C = C~ * this after the tile's update (used for the final state)
+    }
+}
 
+// ---------------------------------------------------------------------------
+// main kernel (general gates)
+// ---------------------------------------------------------------------------
 enum { B_QFULL = 0, B_KFULL, B_VFULL, B_SDONE, B_H1DONE, B_UPDDONE, B_H2DONE, B_QSCALED, B_KSCALED, B_CBREADY,
        B_PREADY, B_HFREE, B_NDONE, B_KREAD, B_HSTAGED, B_VFREE, B_QNDONE, B_NBARS };
-
-__device__ __forceinline__ float ex2_approx(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-// x * w for a packed pair of bf16, w = whi + wlo given as two packed bf16 pairs: rn(x*whi + rn(x*wlo)).
-// Within 2^-16 of the correctly rounded product with the fp32 factor, at 2 instructions per pair.
-__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t x, uint32_t whi2, uint32_t wlo2) {
-    const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162 *>(&x);
-    const __nv_bfloat162 r = __hfma2(xv, *reinterpret_cast<const __nv_bfloat162 *>(&whi2),
-                                     __hmul2(xv, *reinterpret_cast<const __nv_bfloat162 *>(&wlo2)));
-    return *reinterpret_cast<const uint32_t *>(&r);
-}
-__device__ __forceinline__ void split_scale(float w, uint32_t &whi2, uint32_t &wlo2) {
-    const float hi = __bfloat162float(__float2bfloat16_rn(w));
-    whi2 = pack_bf16(hi, hi);
-    wlo2 = pack_bf16(w - hi, w - hi);
-}
-__device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
-    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
-}
-
-// q~ . n for all rows from the RAW Q tile (before it is scaled in place): the dot product q . n is taken
-// in fp32 from the exact bf16 inputs and multiplied by the row scale afterwards, so the state part of the
-// normaliser carries no bf16 rounding of Q~ (it matters where q . n cancels).  Lane mapping: lane = (g, c) with
-// c the physical 16-byte chunk and g a row group; a warp owns the rows with (row & 7) in {2w, 2w+1}, so
-// for a fixed residue rho every lane always meets the same LOGICAL chunk c ^ rho: its 8 values of n are
-// loaded once per (rho, box) and the tile loads are 4 x 128 contiguous bytes per instruction.
-template <int DQK>
-__device__ __forceinline__ void qn_pass(const unsigned char *smem, const float *s_n, float *s_qn, const float *row_scale,
-                                        int wl, int lane) {
-    using SM = Smem<DQK>;
-    constexpr int NBOX = SM::NBOX;
-    const int c = lane & 7, g = lane >> 3;
-    float part[2][4];
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        const int rho = 2 * wl + rr;
-        const int row0 = rho + 8 * g;                 // rows row0 + 32 i
-#pragma unroll
-        for (int i = 0; i < 4; ++i) part[rr][i] = 0.f;
-#pragma unroll
-        for (int q = 0; q < NBOX; ++q) {
-            const float *np = s_n + q * 64 + ((c ^ rho) << 3);
-            const float4 na = *reinterpret_cast<const float4 *>(np);
-            const float4 nb = *reinterpret_cast<const float4 *>(np + 4);
-            const unsigned char *base = smem + SM::Q + q * SM::BOX + row0 * 128 + (c << 4);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint4 v = *reinterpret_cast<const uint4 *>(base + i * 32 * 128);
-                const float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
-                part[rr][i] += (f0.x * na.x + f0.y * na.y + f1.x * na.z + f1.y * na.w) +
-                               (f2.x * nb.x + f2.y * nb.y + f3.x * nb.z + f3.y * nb.w);
-            }
-        }
-    }
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float v = part[rr][i];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            if (c == 0) {
-                const int row = (2 * wl + rr) + 8 * g + 32 * i;
-                s_qn[row] = v * row_scale[row];
-            }
-        }
-}
-
-// In-place row scaling of a [128 x DQK] bf16 tile (boxes of 64 columns, 128-byte swizzle): thread = row,
-// 16-byte chunks visited in a rotated order so that the 8 lanes of a quarter-warp hit 8 different banks.
-template <int DQK>
-__device__ __forceinline__ void scale_rows(unsigned char *tile, int row, float w) {
-    using SM = Smem<DQK>;
-    uint32_t whi, wlo;
-    split_scale(w, whi, wlo);
-#pragma unroll 2
-    for (int q = 0; q < SM::NBOX; ++q) {
-        unsigned char *rowp = tile + q * SM::BOX + row * 128;
-        uint4 v[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4 *>(rowp + (((c + row) & 7) << 4));
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            v[c].x = scale_bf16x2(v[c].x, whi, wlo); v[c].y = scale_bf16x2(v[c].y, whi, wlo);
-            v[c].z = scale_bf16x2(v[c].z, whi, wlo); v[c].w = scale_bf16x2(v[c].w, whi, wlo);
-        }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(rowp + (((c + row) & 7) << 4)) = v[c];
-    }
-}
-
-// One 128-row half of the initial state: global fp32 -> Cb (bf16, swizzled MN-major) and TMEM
-// (pre-scaled by the first tile's decay).  `src` is this thread's row (NULL = zero state).
-template <int DQK>
-__device__ __forceinline__ void c_init_half(unsigned char *smem, uint32_t t_half, const float *src, int j, float decay0) {
-    using SM = Smem<DQK>;
-#pragma unroll 1
-    for (int c0 = 0; c0 < DVS; c0 += 32) {
-        uint32_t v[32];
-#pragma unroll
-        for (int x = 0; x < 32; x += 4) {
-            float4 f = src ? *reinterpret_cast<const float4 *>(src + c0 + x) : make_float4(0.f, 0.f, 0.f, 0.f);
-            v[x] = __float_as_uint(f.x); v[x + 1] = __float_as_uint(f.y);
-            v[x + 2] = __float_as_uint(f.z); v[x + 3] = __float_as_uint(f.w);
-        }
-#pragma unroll
-        for (int x = 0; x < 32; x += 8) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
-            o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
-            o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
-            o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
-            const int c = c0 + x;
-            *reinterpret_cast<uint4 *>(smem + SM::CB + (c >> 6) * SM::CB_BLOCK + sw128_off(j, c & 63)) = o;
-        }
-#pragma unroll
-        for (int x = 0; x < 32; ++x) v[x] = __float_as_uint(__uint_as_float(v[x]) * decay0);
-        tmem_st32(t_half + c0, v);
-    }
-}
 
 // C pass for one 128-row half after the state update: TMEM -> Cb (bf16) and back to TMEM scaled by
 // the next tile's decay; after the last tile the fp32 rows go to `dst` instead.
@@ -393,6 +287,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.x, b = bh / p.NH, hd = bh % p.NH;
+    if (p.path[bh] != 0) return;   // this head runs in the bounded-spread kernel (CTA-uniform, before any set-up)
     const int col0 = blockIdx.y * DVS;
     const int NCH = p.NCH;
     const float *gbase = p.gates + (size_t)bh * NCH * GW;
@@ -721,7 +616,7 @@ bool mlstm_chunkwise_tc_shape_ok(const ChunkwiseParams &p, int dtype) {
     if (dtype != XLSTM_BF16) return false;
     if (p.dqk != 256 && p.dqk != 128) return false;
     if (p.dv % DVS) return false;
-    if (p.S < LT || p.S / LT > 6000) return false;  // gate pre-pass keeps 32 bytes per tile in shared memory
+    if (p.S < LT || p.S / LT > 65535 * (GP_THREADS / 32)) return false;   // grid of the gate pre-pass
     for (int d = 0; d < 3; ++d)
         if (p.sq[d] % 8 || p.sk[d] % 8 || p.sv[d] % 8 || p.sh[d] % 8) return false;  // 16-byte TMA / store alignment
     if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
@@ -741,8 +636,18 @@ size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L
     (void)dv; (void)L;
     const size_t nch = (size_t)(S / LT);
     // header (status) + gate scalars + hand-over state (n, m) for a tail that runs on the exact path
-    return WS_HEADER + (size_t)B * NH * nch * GW * sizeof(float) + (size_t)B * NH * (dqk + 1) * sizeof(float) + 256;
+    // + one path flag per (batch, head) + the chain scratch of the gate pre-pass
+    size_t bytes = WS_HEADER + (size_t)B * NH * nch * GW * sizeof(float) + (size_t)B * NH * (dqk + 1) * sizeof(float) +
+                   (size_t)B * NH * sizeof(int);
+    bytes = (bytes + 255) & ~(size_t)255;
+    return bytes + (size_t)B * NH * nch * GC * sizeof(double) + 256;
 }
+
+namespace {
+std::atomic<int> g_general_only{0};
+}
+
+void mlstm_chunkwise_tc_set_general_only(int on) { g_general_only.store(on ? 1 : 0); }
 
 int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspace_bytes, cudaStream_t st) {
     const int s_full = (p.S / LT) * LT;
@@ -755,19 +660,22 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
     float *gates = reinterpret_cast<float *>(ws + WS_HEADER);
     float *tail_n = gates + (size_t)BH * nch * GW;
     float *tail_m = tail_n + (size_t)BH * p.dqk;
+    int *path = reinterpret_cast<int *>(tail_m + BH);
+    const size_t chain_off = (static_cast<size_t>(reinterpret_cast<unsigned char *>(path + BH) - ws) + 255) & ~(size_t)255;
+    double *chain = reinterpret_cast<double *>(ws + chain_off);
     const bool tail = s_full < p.S;
     if (tail && p.n_peer) return XLSTM_ERR_UNSUPPORTED;   // the exact tail path writes the local h only
     if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return XLSTM_ERR_CUDA;
 
     {
-        auto gk = mlstm_gate_prep_kernel<__nv_bfloat16>;
-        const size_t gsm = 4 * (size_t)nch * sizeof(double);
-        if (gsm > 48 * 1024 &&
-            cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsm) != cudaSuccess)
-            return XLSTM_ERR_CUDA;
-        gk<<<BH, GP_THREADS, gsm, st>>>(static_cast<const __nv_bfloat16 *>(p.ig), static_cast<const __nv_bfloat16 *>(p.fg),
-                                        p.sg[0], p.sg[1], p.sg[2], p.C0 ? p.m0 : nullptr, gates, tail ? tail_m : p.m1,
-                                        p.NH, nch, p.qscale, p.gate_cap);
+        const __nv_bfloat16 *ig = static_cast<const __nv_bfloat16 *>(p.ig), *fg = static_cast<const __nv_bfloat16 *>(p.fg);
+        const dim3 tg((nch + GP_THREADS / 32 - 1) / (GP_THREADS / 32), BH);
+        mlstm_gate_stats_kernel<__nv_bfloat16><<<tg, GP_THREADS, 0, st>>>(ig, fg, p.sg[0], p.sg[1], p.sg[2], chain, p.NH, nch,
+                                                                          p.gate_cap);
+        mlstm_gate_chain_kernel<<<BH, 32, 0, st>>>(p.C0 ? p.m0 : nullptr, chain, tail ? tail_m : p.m1, path, nch,
+                                                   g_general_only.load());
+        mlstm_gate_write_kernel<__nv_bfloat16><<<tg, GP_THREADS, 0, st>>>(ig, fg, p.sg[0], p.sg[1], p.sg[2], chain, path, gates,
+                                                                          p.NH, nch, p.qscale, p.gate_cap);
     }
     if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
 
@@ -784,7 +692,13 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
             return XLSTM_ERR_UNSUPPORTED;
     tp.C1 = p.C1; tp.n1 = tail ? tail_n : p.n1;
     tp.NH = p.NH; tp.dv = p.dv; tp.NCH = nch; tp.eps = p.eps; tp.log2_qscale = log2f(p.qscale); tp.status = status;
+    tp.path = path; tp.h = p.h;
+    for (int d = 0; d < 3; ++d) tp.sh[d] = p.sh[d];
     dim3 grid(BH, p.dv / DVS);
+    // Two launches over the same grid: every CTA looks at its head's path flag (written by the pre-pass) and
+    // returns at once if the head belongs to the other kernel, so the choice needs no host round trip.
+    const int rc = mlstm_chunkwise_tc_fast_launch(tp, grid, p.dqk, st);
+    if (rc != XLSTM_OK) return rc;
     cudaError_t e;
     if (p.dqk == 256) {
         auto kern = mlstm_chunkwise_tc_kernel<256>;

@@ -285,6 +285,7 @@ static int slstm_recurrent_launch(const void *gx, const void *R, const float *rb
 namespace xl {
 // tensor-core version (slstm_tc.cu): bf16, head dimension 256
 bool slstm_recurrent_tc_supported(int dtype, int dh, const void *R, const void *gx, const void *hs);
+int slstm_recurrent_tc_status(cudaStream_t st);
 int slstm_recurrent_tc(const void *gx, const void *R, const float *rb, const float *c0, const float *n0, const float *h0,
                        const float *m0, void *hs, float *c1, float *n1, float *h1, float *m1, int B, int S, int NH,
                        float cap, cudaStream_t st);
@@ -327,4 +328,8 @@ extern "C" int xlstm_slstm_recurrent(const void *gx, const void *R, const float 
     if (dtype == XLSTM_F32)
         return xl::slstm_recurrent_launch<float>(gx, R, rb, c0, n0, h0, m0, hs, c1, n1, h1, m1, B, S, NH, dh, cap, st);
     return xl::slstm_recurrent_launch<__nv_bfloat16>(gx, R, rb, c0, n0, h0, m0, hs, c1, n1, h1, m1, B, S, NH, dh, cap, st);
+}
+
+extern "C" int xlstm_slstm_recurrent_status(void *stream) {
+    return xl::slstm_recurrent_tc_status(static_cast<cudaStream_t>(stream));
 }

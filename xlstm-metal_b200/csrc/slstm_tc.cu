@@ -26,6 +26,9 @@ namespace xl {
 namespace {
 using namespace tc;
 
+// set by any CTA whose bounded wait gave up; read and cleared by slstm_recurrent_tc_status()
+__device__ int g_tcr_timeout = 0;
+
 constexpr int TCR_THREADS = 512;
 constexpr int TCR_U = 64;      // units per CTA
 constexpr int TCR_DH = 256;    // head dimension = K of the MMA
@@ -317,6 +320,7 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
         }
     }
     const bool failed = *abort_flag != 0;
+    if (failed && tid == 0) atomicExch(&g_tcr_timeout, 1);
     if (row_ok) {
 #pragma unroll
         for (int e = 0; e < CPT; ++e) {
@@ -330,6 +334,19 @@ slstm_recurrent_tc_kernel(const __nv_bfloat16 *__restrict__ gx, const __nv_bfloa
 }
 
 }  // namespace
+
+int slstm_recurrent_tc_status(cudaStream_t st) {
+    int v = 0;
+    if (cudaMemcpyFromSymbolAsync(&v, g_tcr_timeout, sizeof(int), 0, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+        return XLSTM_ERR_CUDA;
+    if (!v) return XLSTM_OK;
+    const int zero = 0;
+    if (cudaMemcpyToSymbolAsync(g_tcr_timeout, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+        return XLSTM_ERR_CUDA;
+    return XLSTM_ERR_TIMEOUT;
+}
 
 bool slstm_recurrent_tc_supported(int dtype, int dh, const void *R, const void *gx, const void *hs) {
     return dtype == XLSTM_BF16 && dh == TCR_DH &&

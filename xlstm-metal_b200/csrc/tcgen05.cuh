@@ -46,6 +46,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// A 128-thread role group waits on an mbarrier: ONE thread polls, the others sleep on a hardware named
+// barrier (every poll of every warp is a shared-memory access that competes with the tensor cores' operand
+// reads; with all threads polling, the polls alone were a third of a tile's shared-memory wavefronts).
+// The poller publishes the outcome in `res[2]` (alternating slots: a slot is rewritten only two waits later,
+// after every thread has passed the named barrier of the wait in between), so all 128 threads take the same
+// branch even when a time-out or an abort arrives while some of them are already past the barrier.
+struct GroupWait {
+    uint64_t *bars;
+    volatile int *abort_flag;
+    volatile int *res;
+    int bar_id;       // named barrier 1..15 (0 is __syncthreads)
+    bool poller;
+    uint32_t count;
+    __device__ __forceinline__ bool operator()(int idx, uint32_t parity) {
+        const uint32_t slot = count++ & 1u;
+        if (poller) res[slot] = mbar_wait(&bars[idx], parity, abort_flag) ? 1 : 0;
+        // barrier.sync without .aligned: the poller's warp reaches it diverged (lane 0 comes from the poll loop)
+        asm volatile("barrier.sync %0, 128;" ::"r"(bar_id) : "memory");
+        return res[slot] != 0;
+    }
+};
+
 // ---- fences -------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

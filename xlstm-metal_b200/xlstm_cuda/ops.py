@@ -94,6 +94,23 @@ def _strides3(t: torch.Tensor):
     return [t.stride(0), t.stride(1), t.stride(2)]
 
 
+def chunkwise_general_only(on: bool) -> None:
+    """Send every head of the bf16 chunkwise forward to the general tensor-core kernel (``True``) or let the
+    device pick per head between it and the bounded-gate-spread kernel (``False``, the default)."""
+    _lib.load().xlstm_mlstm_chunkwise_set_general_only(1 if on else 0)
+
+
+def chunkwise_status(workspace: Optional[torch.Tensor] = None) -> None:
+    """Raise ``XlstmCudaError`` if a bounded device-side wait of the last chunkwise forward that used
+    ``workspace`` gave up (``None``: the library's built-in block).  Synchronises the current stream."""
+    _lib.check(_lib.load().xlstm_mlstm_chunkwise_status(_ptr(workspace), _stream()), "xlstm_mlstm_chunkwise_status")
+
+
+def slstm_recurrent_status() -> None:
+    """The same for the tensor-core path of ``slstm_recurrent`` (all launches since the last query)."""
+    _lib.check(_lib.load().xlstm_slstm_recurrent_status(_stream()), "xlstm_slstm_recurrent_status")
+
+
 def chunkwise_workspace_bytes(B, NH, S, dqk, dv, L, dtype: torch.dtype) -> int:
     return int(_lib.load().xlstm_mlstm_chunkwise_workspace_bytes(B, NH, S, dqk, dv, L, _DT[dtype]))
 
