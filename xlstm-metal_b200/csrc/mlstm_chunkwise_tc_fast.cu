@@ -28,7 +28,8 @@
 // Roles (640 threads): warp 0 TMA producer, warp 1 MMA issuer (+TMEM alloc), warp 2 TMA stores of the staged h
 // tile (to this GPU and, in head-sharded runs, to every peer); warps 4-7 V~ scaling, gate matrix P and the C pass for rows
 // [128,256); warps 8-11 q . n~ from the raw Q tile; warps 12-15 normaliser update and the C pass for rows
-// [0,128); warps 16-19 epilogue (h tile staged in the V buffer once P V~ has read it).
+// [0,128); warps 16-19 the upper pieces of the gate matrix, then the epilogue (h tile staged in the V buffer
+// once P V~ has read it).
 // Every mbarrier wait is bounded; a time-out sets the status word in the scratch buffer, releases all roles
 // and frees TMEM before the CTA returns.
 #include "mlstm_chunkwise_tc.cuh"
@@ -41,8 +42,9 @@ using namespace tc;
 using namespace tcw;
 
 enum { F_QFULL = 0, F_KFULL, F_VFULL, F_SDONE, F_UPDA, F_UPDB, F_PVDONE, F_VSCALED, F_PREADY, F_CBA, F_CBB,
-       F_HFREE, F_QNDONE, F_NDONE, F_HSTAGED, F_VFREE, F_NBARS };
+       F_HFREE, F_QNDONE, F_NDONE, F_HSTAGED, F_VFREE, F_SAREADY, F_NBARS };
 static_assert(F_NBARS <= 24, "barrier slots");
+constexpr int PREFETCH_AHEAD = 2;   // tiles between the L2 prefetch of a box and the iteration that loads it
 
 // C pass for one 128-row half after the state update: optional rescale of C~ in TMEM, then the bf16 copy
 // Cb (in the frame the next tile reads it in); after the last tile the fp32 rows go to `dst` instead.
@@ -96,6 +98,54 @@ __device__ __forceinline__ void c_pass_fast(unsigned char *smem, uint32_t t_half
     }
 }
 
+// One 32 x 32 piece of the gate matrix: S values in `r` -> causal mask on the diagonal piece, row-sum
+// contribution sum_s S_ts a_s (fp32, before rounding; four independent partial sums) and the bf16 pairs of P.
+// P piece pc is written over the FIRST 16 columns of S piece pc (columns [32 pc, 32 pc + 16)), so a piece
+// never lands on S values that another warp has still to read; the P V~ MMAs address the pieces accordingly.
+__device__ __forceinline__ float p_piece(const uint32_t (&r)[32], uint32_t t_rows, int pc, bool diag, int lane, const float4 *a4) {
+    uint32_t packed[16];
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const float4 a = a4[(pc * 32 + j) >> 2];
+        float p0 = __uint_as_float(r[j]), p1 = __uint_as_float(r[j + 1]);
+        float p2 = __uint_as_float(r[j + 2]), p3 = __uint_as_float(r[j + 3]);
+        if (diag) {
+            if (j > lane) p0 = 0.f;
+            if (j + 1 > lane) p1 = 0.f;
+            if (j + 2 > lane) p2 = 0.f;
+            if (j + 3 > lane) p3 = 0.f;
+        }
+        s0 = fmaf(p0, a.x, s0); s1 = fmaf(p1, a.y, s1);
+        s2 = fmaf(p2, a.z, s2); s3 = fmaf(p3, a.w, s3);
+        packed[j >> 1] = pack_bf16(p0, p1);
+        packed[(j >> 1) + 1] = pack_bf16(p2, p3);
+    }
+    tmem_st16(t_rows + pc * 32, packed);
+    return (s0 + s1) + (s2 + s3);
+}
+
+// The gate-matrix pass is shared by TWO warps per block of 32 rows (the triangle gives row block q the pieces
+// 0..q, so one warp per block would leave the last block with four pieces and the first with one): the "lower"
+// warp takes the pieces [0, nl), the "upper" warp [nl, q] and zero-fills the pieces above the diagonal, with
+// nl = (q + 2) / 2: at most two pieces per warp.  This function does the pieces [first, last) and zero-fills
+// [zfirst, 4); it returns the warp's part of the row sums of tril(S) diag(a).
+__device__ __forceinline__ float p_pass_part(uint32_t t_rows, int q, int lane, const float4 *a4, int first, int last,
+                                             int zfirst) {
+    float rowsum = 0.f;
+    uint32_t r[32];
+    for (int pc = first; pc < last; ++pc) {
+        tmem_ld32(t_rows + pc * 32, r);
+        tmem_wait_ld();
+        rowsum += p_piece(r, t_rows, pc, pc == q, lane, a4);
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = 0u;
+    for (int pc = zfirst; pc < 4; ++pc) tmem_st16(t_rows + pc * 32, reinterpret_cast<const uint32_t (&)[16]>(r));
+    tmem_wait_st();
+    return rowsum;
+}
+
 template <int DQK>
 __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(const __grid_constant__ TcParams p) {
     using SM = Smem<DQK>;
@@ -125,9 +175,10 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
         mbar_init(&bars[F_QFULL], 1);    mbar_init(&bars[F_KFULL], 1);    mbar_init(&bars[F_VFULL], 1);
         mbar_init(&bars[F_SDONE], 1);    mbar_init(&bars[F_UPDA], 1);     mbar_init(&bars[F_UPDB], 1);
         mbar_init(&bars[F_PVDONE], 1);
-        mbar_init(&bars[F_VSCALED], 128); mbar_init(&bars[F_PREADY], 128); mbar_init(&bars[F_CBA], 128);
+        mbar_init(&bars[F_VSCALED], 128); mbar_init(&bars[F_PREADY], 256); mbar_init(&bars[F_CBA], 128);
         mbar_init(&bars[F_CBB], 128);     mbar_init(&bars[F_HFREE], 128);  mbar_init(&bars[F_QNDONE], 128);
         mbar_init(&bars[F_NDONE], 128);   mbar_init(&bars[F_HSTAGED], 128); mbar_init(&bars[F_VFREE], 1);
+        mbar_init(&bars[F_SAREADY], 128);
         mbar_fence_init();
         tma_prefetch_desc(&p.tq); tma_prefetch_desc(&p.tk); tma_prefetch_desc(&p.tv);
     }
@@ -136,11 +187,12 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t T_C = tmem, T_S = tmem + 256, T_H = tmem + 384;
-    // role groups of 128 threads (warps 4-7, 8-11, 12-15, 16-19) wait through one polling thread each
-    const int grp = (warp >> 2) - 1;
-    GroupWait gwait{bars, abort_flag, reinterpret_cast<volatile int *>(&bars[20]) + 2 * (grp < 0 ? 0 : grp), 1 + grp,
-                    (tid & 127) == 0, 0u};
+    // S/P and H swap their two 128-column regions every tile: the read-out of tile k+1 accumulates where S/P of
+    // tile k lived (free as soon as P V~ of tile k has run, in issue order) instead of waiting for the epilogue to
+    // drain H of tile k; only S of tile k+1, issued a group later, needs the drained region.
+    const uint32_t T_C = tmem;
+    auto t_s = [tmem](int k) -> uint32_t { return tmem + 256 + 128 * (k & 1); };
+    auto t_h = [tmem](int k) -> uint32_t { return tmem + 384 - 128 * (k & 1); };
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -150,6 +202,14 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
             for (int k = 0; k < NCH; ++k) {
                 const int t0 = k * LT;
                 const uint32_t pp = (k - 1) & 1;
+                // A load that misses L2 takes 2-3 k clocks from issue to completion (DRAM latency, whatever its
+                // size), more than the window in which a single-buffered tile is free: the boxes of the tile after
+                // the next one are pulled into L2 here, a tile and a half before their loads are issued.
+                if (k + PREFETCH_AHEAD < NCH) {
+                    const int tp = (k + PREFETCH_AHEAD) * LT;
+                    for (int q = 0; q < NBOX; ++q) { tma_prefetch_4d(&p.tq, q * 64, tp, hd, b); tma_prefetch_4d(&p.tk, q * 64, tp, hd, b); }
+                    for (int q = 0; q < 2; ++q) tma_prefetch_4d(&p.tv, col0 + q * 64, tp, hd, b);
+                }
                 if (k > 0 && !(mbar_wait(&bars[F_SDONE], pp, abort_flag) && mbar_wait(&bars[F_QNDONE], pp, abort_flag))) break;
                 mbar_expect_tx(&bars[F_QFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[F_QFULL], q * 64, t0, hd, b);
@@ -176,8 +236,9 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
             for (int k = 0; k < NCH; ++k) {
                 const uint32_t ph = k & 1;
                 // H = Q Cb, one 128-row half of Cb at a time (the C pass of the other half may still run)
+                // (H goes where S/P of the previous tile was: free, since that tile's P V~ was issued before)
+                const uint32_t T_S = t_s(k), T_H = t_h(k);
                 if (!(mbar_wait(&bars[F_QFULL], ph, abort_flag) && mbar_wait(&bars[F_CBA], ph, abort_flag))) break;
-                if (k > 0 && !mbar_wait(&bars[F_HFREE], (k - 1) & 1, abort_flag)) break;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
@@ -195,6 +256,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
                 }
                 // S = Q K^T (the previous tile's P V~ was issued earlier and finishes first: in-order pipe)
                 if (!mbar_wait(&bars[F_KFULL], ph, abort_flag)) break;
+                if (k > 0 && !mbar_wait(&bars[F_HFREE], (k - 1) & 1, abort_flag)) break;   // S lands where H of the previous tile was
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < DQK / 16; ++kk) {
@@ -216,7 +278,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
                 if (!mbar_wait(&bars[F_PREADY], ph, abort_flag)) break;
                 tc_fence_after_sync();
 #pragma unroll
-                for (int kk = 0; kk < LT / 16; ++kk) mma_ts(T_H, T_S + kk * 8, dV + kk * (2048 >> 4), ID_KM, true);
+                for (int kk = 0; kk < LT / 16; ++kk)   // P piece kk / 2 sits in the first 16 columns of S piece kk / 2
+                    mma_ts(T_H, T_S + (kk >> 1) * 32 + (kk & 1) * 8, dV + kk * (2048 >> 4), ID_KM, true);
                 mma_commit(&bars[F_PVDONE]);
             }
         }
@@ -252,51 +315,20 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
             const uint32_t ph = k & 1;
             const float *g = gbase + (size_t)k * GW;
             // V~ = diag(a) V in place (these warps are idle until S completes; V arrives early in the tile)
-            if (!gwait(F_VFULL, ph)) break;
+            if (!mbar_wait(&bars[F_VFULL], ph, abort_flag)) break;
             scale_tile_rows<2>(smem + SM::V, SM::BOX, t, g[G_W + t]);
             fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor-core (async) proxy
             mbar_arrive(&bars[F_VSCALED]);
-            if (!(gwait(F_QNDONE, ph) && gwait(F_SDONE, ph))) break;
+            if (!(mbar_wait(&bars[F_SAREADY], ph, abort_flag) && mbar_wait(&bars[F_SDONE], ph, abort_flag))) break;
             tc_fence_after_sync();
-            float rowsum = 0.f;
-#pragma unroll
-            for (int pc = 0; pc < 4; ++pc) {
-                const int s0 = pc * 32;
-                uint32_t packed[16];
-                if (s0 <= t0w) {  // warp-uniform; columns beyond the warp's rows are all masked
-                    uint32_t r[32];
-                    tmem_ld32(T_S + lane_off + s0, r);
-                    tmem_wait_ld();
-                    const bool diag = (s0 == t0w);
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const float4 a = a4[(s0 + j) >> 2];
-                        float p0 = __uint_as_float(r[j]), p1 = __uint_as_float(r[j + 1]);
-                        float p2 = __uint_as_float(r[j + 2]), p3 = __uint_as_float(r[j + 3]);
-                        if (diag) {
-                            if (j > lane) p0 = 0.f;
-                            if (j + 1 > lane) p1 = 0.f;
-                            if (j + 2 > lane) p2 = 0.f;
-                            if (j + 3 > lane) p3 = 0.f;
-                        }
-                        rowsum = fmaf(p0, a.x, rowsum); rowsum = fmaf(p1, a.y, rowsum);
-                        rowsum = fmaf(p2, a.z, rowsum); rowsum = fmaf(p3, a.w, rowsum);
-                        packed[j >> 1] = pack_bf16(p0, p1);
-                        packed[(j >> 1) + 1] = pack_bf16(p2, p3);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) packed[j] = 0u;
-                }
-                tmem_st16(T_S + lane_off + (s0 >> 1), packed);
-            }
-            tmem_wait_st();
+            // the lower pieces of this row block; the epilogue warp of the same rows takes the rest
+            const float rowsum = p_pass_part(t_s(k) + lane_off, warp & 3, lane, a4, 0, ((warp & 3) + 2) >> 1, 4);
             s_rs[t] = rowsum;   // read by the epilogue warps after PREADY
             tc_fence_before_sync();
             mbar_arrive(&bars[F_PREADY]);
             if (NHALF == 2) {
                 const bool last = (k == NCH - 1);
-                if (!gwait(F_UPDB, ph)) break;
+                if (!mbar_wait(&bars[F_UPDB], ph, abort_flag)) break;
                 tc_fence_after_sync();
                 c_pass_fast<DQK>(smem, T_C + 128 + lane_off, 128 + t, last, g[G_SCAL + 0], g[G_SCAL + 2],
                                  p.C1 + ((size_t)bh * DQK + 128 + t) * p.dv + col0);
@@ -315,10 +347,11 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
             const uint32_t ph = k & 1;
             const float a = gbase[(size_t)k * GW + G_W + t];
             // the previous epilogue has read s_qn and the previous P pass / normaliser update have read s_a
-            if (k > 0 && !gwait(F_HFREE, (k - 1) & 1)) break;
-            if (!gwait(F_NDONE, ph)) break;    // n~ before this tile is final
+            if (k > 0 && !mbar_wait(&bars[F_HFREE], (k - 1) & 1, abort_flag)) break;
+            if (!mbar_wait(&bars[F_NDONE], ph, abort_flag)) break;    // n~ before this tile is final
             s_a[t] = a;
-            if (!gwait(F_QFULL, ph)) break;
+            mbar_arrive(&bars[F_SAREADY]);   // the gate-matrix warps need a_s, not q . n~
+            if (!mbar_wait(&bars[F_QFULL], ph, abort_flag)) break;
             qn_pass<DQK>(smem, s_n, s_qn, nullptr, warp - 8, lane);
             mbar_arrive(&bars[F_QNDONE]);
         }
@@ -342,7 +375,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
             const float *g = gbase + (size_t)k * GW;
             const bool last = (k == NCH - 1);
             const float mul = g[G_SCAL + 0], frame = g[G_SCAL + 2];
-            if (!(gwait(F_KFULL, ph) && gwait(F_QNDONE, ph))) break;
+            if (!(mbar_wait(&bars[F_KFULL], ph, abort_flag) && mbar_wait(&bars[F_QNDONE], ph, abort_flag))) break;
             if (q < NBOX) {
                 const unsigned char *box = smem + SM::K + q * SM::BOX + ((cp & 3) << 2);
                 float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -367,7 +400,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
                 }
             }
             mbar_arrive(&bars[F_NDONE]);   // K no longer read by the CUDA cores; n~ after this tile is final
-            if (!gwait(F_UPDA, ph)) break;
+            if (!mbar_wait(&bars[F_UPDA], ph, abort_flag)) break;
             tc_fence_after_sync();
             c_pass_fast<DQK>(smem, T_C + lane_off, r, last, mul, frame, p.C1 + ((size_t)bh * DQK + r) * p.dv + col0);
             if (!last) {
@@ -378,41 +411,56 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
             }
         }
     } else if (warp >= 16) {
-        // ================= epilogue: h = winq H' / (max(|den|, e^{-m_t}) + eps) =================
-        const int r = tid - 512;                         // token row of H = TMEM lane
+        // ================= upper pieces of the gate matrix; epilogue: h = winq H' / (max(|den|, e^{-m_t}) + eps) =================
+        const int r = tid - 512;                         // token row of S and H = TMEM lane
         const uint32_t lane_off = (uint32_t)(r & ~31) << 16;
+        const float4 *a4 = reinterpret_cast<const float4 *>(s_a);
+        const int q = warp & 3;
         for (int k = 0; k < NCH; ++k) {
             const uint32_t ph = k & 1;
             const float *g = gbase + (size_t)k * GW;
             const float winq = g[G_WINQ + r], emt = g[G_EMT + r];
-            if (!(gwait(F_QNDONE, ph) && gwait(F_PREADY, ph) &&
-                  gwait(F_PVDONE, ph))) break;
+            if (!(mbar_wait(&bars[F_SAREADY], ph, abort_flag) && mbar_wait(&bars[F_SDONE], ph, abort_flag))) break;
             tc_fence_after_sync();
-            const float den = winq * (s_qn[r] + s_rs[r]);
-            const float inv = winq / (fmaxf(fabsf(den), emt) + p.eps);
-            // the whole row goes to registers as packed bf16 first, so that H is released for the next tile's
-            // read-out before any store is issued
-            uint32_t hp[DVS / 2];
-#pragma unroll
-            for (int c0 = 0; c0 < DVS; c0 += 32) {
-                uint32_t va[32];
-                tmem_ld32(T_H + lane_off + c0, va);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 32; j += 2)
-                    hp[(c0 + j) >> 1] = pack_bf16(__uint_as_float(va[j]) * inv, __uint_as_float(va[j + 1]) * inv);
-            }
+            const float rs_upper = p_pass_part(t_s(k) + lane_off, q, lane, a4, (q + 2) >> 1, q + 1, q + 1);
             tc_fence_before_sync();
-            mbar_arrive(&bars[F_HFREE]);          // H (and s_qn, s_rs) have been read
-            // swizzled box layout of the h tensor maps, in the V buffer (idle: update and P V~ have completed).
-            // Direct 16-byte stores from these registers to global memory were measured slower: 32 rows per
-            // instruction keep the load/store unit busy for ~2.5 k clocks per tile and stall every other
-            // warp's shared-memory accesses.
+            mbar_arrive(&bars[F_PREADY]);
+            if (!(mbar_wait(&bars[F_QNDONE], ph, abort_flag) && mbar_wait(&bars[F_PREADY], ph, abort_flag) &&
+                  mbar_wait(&bars[F_PVDONE], ph, abort_flag))) break;
+            tc_fence_after_sync();
+            const float den = winq * (s_qn[r] + s_rs[r] + rs_upper);
+            const float inv = winq / (fmaxf(fabsf(den), emt) + p.eps);
+            // H -> bf16 h tile staged in the V buffer (idle: update and P V~ of this tile have completed), in the
+            // swizzled box layout of the h tensor maps.  (Direct 16-byte stores from registers to global memory
+            // were measured slower: 32 rows per instruction keep the load/store unit busy for ~2.5 k clocks per
+            // tile and stall every other warp's shared-memory accesses.)
             unsigned char *stage = smem + SM::V + r * 128;
+#pragma unroll 1
+            for (int c0 = 0; c0 < DVS; c0 += 64) {
+                uint32_t va[32], vb[32];
+                tmem_ld32(t_h(k) + lane_off + c0, va);
+                tmem_ld32(t_h(k) + lane_off + c0 + 32, vb);
+                tmem_wait_ld();
+                if (c0 == DVS - 64) {                 // H (and s_qn, s_rs) have been read: the next tile may proceed
+                    tc_fence_before_sync();
+                    mbar_arrive(&bars[F_HFREE]);
+                }
+                unsigned char *box = stage + (c0 >> 6) * SM::BOX;
 #pragma unroll
-            for (int c = 0; c < DVS / 8; ++c)
-                *reinterpret_cast<uint4 *>(stage + (c >> 3) * SM::BOX + (((c & 7) ^ (r & 7)) << 4)) =
-                    make_uint4(hp[4 * c], hp[4 * c + 1], hp[4 * c + 2], hp[4 * c + 3]);
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 o;
+                    o.x = pack_bf16(__uint_as_float(va[j]) * inv, __uint_as_float(va[j + 1]) * inv);
+                    o.y = pack_bf16(__uint_as_float(va[j + 2]) * inv, __uint_as_float(va[j + 3]) * inv);
+                    o.z = pack_bf16(__uint_as_float(va[j + 4]) * inv, __uint_as_float(va[j + 5]) * inv);
+                    o.w = pack_bf16(__uint_as_float(va[j + 6]) * inv, __uint_as_float(va[j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(box + ((((j >> 3)) ^ (r & 7)) << 4)) = o;
+                    o.x = pack_bf16(__uint_as_float(vb[j]) * inv, __uint_as_float(vb[j + 1]) * inv);
+                    o.y = pack_bf16(__uint_as_float(vb[j + 2]) * inv, __uint_as_float(vb[j + 3]) * inv);
+                    o.z = pack_bf16(__uint_as_float(vb[j + 4]) * inv, __uint_as_float(vb[j + 5]) * inv);
+                    o.w = pack_bf16(__uint_as_float(vb[j + 6]) * inv, __uint_as_float(vb[j + 7]) * inv);
+                    *reinterpret_cast<uint4 *>(box + ((((j >> 3) + 4) ^ (r & 7)) << 4)) = o;
+                }
+            }
             fence_proxy_async_smem();
             mbar_arrive(&bars[F_HSTAGED]);
         }

@@ -46,28 +46,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
-// A 128-thread role group waits on an mbarrier: ONE thread polls, the others sleep on a hardware named
-// barrier (every poll of every warp is a shared-memory access that competes with the tensor cores' operand
-// reads; with all threads polling, the polls alone were a third of a tile's shared-memory wavefronts).
-// The poller publishes the outcome in `res[2]` (alternating slots: a slot is rewritten only two waits later,
-// after every thread has passed the named barrier of the wait in between), so all 128 threads take the same
-// branch even when a time-out or an abort arrives while some of them are already past the barrier.
-struct GroupWait {
-    uint64_t *bars;
-    volatile int *abort_flag;
-    volatile int *res;
-    int bar_id;       // named barrier 1..15 (0 is __syncthreads)
-    bool poller;
-    uint32_t count;
-    __device__ __forceinline__ bool operator()(int idx, uint32_t parity) {
-        const uint32_t slot = count++ & 1u;
-        if (poller) res[slot] = mbar_wait(&bars[idx], parity, abort_flag) ? 1 : 0;
-        // barrier.sync without .aligned: the poller's warp reaches it diverged (lane 0 comes from the poll loop)
-        asm volatile("barrier.sync %0, 128;" ::"r"(bar_id) : "memory");
-        return res[slot] != 0;
-    }
-};
-
 // ---- fences -------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -83,6 +61,12 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// 4-D tile prefetch into L2 (no shared-memory destination, no barrier): the later load of the same box hits L2
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *m, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+                 ::"l"(m), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
 // 4-D tile store shared -> global (bulk async group); the source tile must stay untouched until
