@@ -108,6 +108,19 @@ size_t xlstm_mlstm_chunkwise_workspace_bytes(int B, int NH, int S, int dqk, int 
 int xlstm_mlstm_chunkwise_set_general_only(int on);
 
 /*
+ * Segment-parallel prefill.  One persistent CTA per (batch, head, 128 dv columns) walks the whole sequence, so
+ * a call with few heads (a head-sharded rank, a single prompt) leaves most SMs idle.  The carry (decay, m, C, n)
+ * of the recurrence is associative: the forward then cuts every sequence into P segments, runs all segments
+ * from an empty state to get their local end states, combines those into the true state at the start of every
+ * segment, and runs all segments again from there - two passes over 1/P of the sequence per CTA.  P is chosen
+ * from the grid size (1 when the grid already fills the GPU); xlstm_mlstm_chunkwise_workspace_bytes() includes
+ * the segment states, and a forward whose scratch only holds the single-pass amount runs the single pass.
+ * segments >= 1 forces P (process-wide; tests and comparisons), < 1 restores the automatic choice.
+ * No counterpart in the reference (its chunk loop is sequential: .../mlstm_chunkwise_recurrent_fw_C_kernel.metal:156-299).
+ */
+int xlstm_mlstm_chunkwise_set_segments(int segments);
+
+/*
  * xlstm_mlstm_chunkwise_fwd fused with the all-gather of h for head-sharded execution: the
  * epilogue stores every h tile to `h` AND, with the same strides and offsets, to `n_peers` (<= 7)
  * further base pointers - the same head slot of the peer GPUs' [B,S,NH_total,dv] buffers, mapped

@@ -425,3 +425,37 @@ def test_gate_cap_inside_the_kernels(ops, dtype, shape):
     h1, _ = ops.mlstm_chunkwise(dev(q, dtype), dev(k, dtype), dev(v, dtype), dev(i_cap, dtype), dev(f_cap, dtype), None, 64, 1e-6,
                                 gate_cap=0.0)
     assert torch.equal(h0, h1)
+
+
+@pytest.mark.parametrize("general", [False, True])
+def test_chunkwise_segment_parallel_equals_single_pass(ops, general):
+    """The segment-parallel two-pass mode (every segment from an empty state, states combined, every segment again
+    from its true start state) against the single pass and against the oracle: bf16 tensor-core shapes, with a
+    carried-in state and a sequence tail, for segment counts that divide the tiles evenly and unevenly."""
+    rng = np.random.default_rng(21)
+    B, NH, S, dqk, dv = 1, 2, 2048 + 70, 256, 256
+    q, k = (xo.bf16_round(rng.standard_normal((B, NH, S, dqk)).astype(np.float32)) for _ in range(2))
+    v = xo.bf16_round(rng.standard_normal((B, NH, S, dv)).astype(np.float32))
+    i, f = (xo.bf16_round(a) for a in gates(rng, (B, NH, S)))
+    st0 = ((rng.standard_normal((B, NH, dqk, dv)) * 0.1).astype(np.float32),
+           (rng.standard_normal((B, NH, dqk)) * 0.1).astype(np.float32), rng.standard_normal((B, NH)).astype(np.float32))
+    h_ref, st_ref = xo.mlstm_recurrent(q, k, v, i, f, st0)
+    args = [dev(a, torch.bfloat16) for a in (q, k, v, i, f)]
+    std = tuple(dev(a) for a in st0)
+    try:
+        ops.chunkwise_general_only(general)
+        ops.chunkwise_segments(1)
+        h1, s1 = ops.mlstm_chunkwise(*args, state=std)
+        for P in (2, 3, 4, 16):
+            ops.chunkwise_segments(P)
+            h, s = ops.mlstm_chunkwise(*args, state=std)
+            assert relerr(host(h), h_ref) < BF16_TOL and relerr(host(h), host(h1)) < BF16_TOL, P
+            assert relerr(host(s[0]), st_ref[0]) < BF16_TOL and relerr(host(s[1]), st_ref[1]) < BF16_TOL, P
+            assert np.abs(host(s[2]) - st_ref[2]).max() < 1e-3, P
+            assert relerr(host(s[0]), host(s1[0])) < 5e-3, P
+        ops.chunkwise_segments(None)     # planned from the grid size: 4 CTAs on 148 SMs -> segments
+        h, s = ops.mlstm_chunkwise(*args, state=std)
+        assert relerr(host(h), h_ref) < BF16_TOL and relerr(host(s[0]), st_ref[0]) < BF16_TOL
+    finally:
+        ops.chunkwise_segments(None)
+        ops.chunkwise_general_only(False)

@@ -29,9 +29,14 @@ bool mlstm_chunkwise_tc_shape_ok(const ChunkwiseParams &p, int dtype);
 bool mlstm_chunkwise_tc_driver_ok();
 bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype);
 size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L);
+// scratch of the single-pass mode (no segment states): what the forward needs at least
+size_t mlstm_chunkwise_tc_workspace_min(int B, int NH, int S, int dqk, int dv);
 int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspace_bytes, cudaStream_t st);
 // 1: every head takes the general tensor-core kernel whatever its gates are; 0: per-head choice (default)
 void mlstm_chunkwise_tc_set_general_only(int on);
+// segments >= 1: cut every sequence into that many segments (segment-parallel two-pass mode); < 1: planned from
+// the grid size (default)
+void mlstm_chunkwise_tc_set_segments(int segments);
 
 int mlstm_chunkwise_static_scratch(void **out);
 

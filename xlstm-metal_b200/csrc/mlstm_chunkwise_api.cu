@@ -21,6 +21,11 @@ extern "C" int xlstm_mlstm_chunkwise_set_general_only(int on) {
     return XLSTM_OK;
 }
 
+extern "C" int xlstm_mlstm_chunkwise_set_segments(int segments) {
+    xl::mlstm_chunkwise_tc_set_segments(segments);
+    return XLSTM_OK;
+}
+
 extern "C" int xlstm_mlstm_chunkwise_status(const void *workspace, void *stream) {
     const void *ws = workspace;
     if (!ws) {
@@ -87,7 +92,7 @@ static int chunkwise_dispatch(const void *q, const void *k, const void *v, const
     // state) on the exact path: the split the reference neuron makes between its chunkwise and
     // recurrent cells (mlx_jit/.../mlstm_neuron.py:222-257).  The tile size is internal: the
     // chunkwise form is a re-association of the recurrence and its result does not depend on L.
-    const size_t need = xl::mlstm_chunkwise_tc_workspace(B, NH, S, dqk, dv, L);
+    const size_t need = xl::mlstm_chunkwise_tc_workspace_min(B, NH, S, dqk, dv);
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return XLSTM_ERR_WORKSPACE;
     return xl::mlstm_chunkwise_tc(p, workspace, workspace_bytes, st);

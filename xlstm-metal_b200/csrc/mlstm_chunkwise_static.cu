@@ -88,7 +88,7 @@ extern "C" int xlstm_mlstm_chunkwise_fwd_static(const void *q, const void *k, co
     if (!xl::mlstm_chunkwise_tc_shape_ok(p, dtype)) return xl::mlstm_chunkwise_simt(p, dtype, st);
 
     // size check before anything else can launch: a problem beyond the block is an error, never a fallback
-    const size_t need = xl::mlstm_chunkwise_tc_workspace(B, NH, S, dqk, dv, L);
+    const size_t need = xl::mlstm_chunkwise_tc_workspace_min(B, NH, S, dqk, dv);   // the block is used by the single-pass mode
     if (need > XLSTM_STATIC_SCRATCH_BYTES) return XLSTM_ERR_STATIC_SCRATCH;
     if (!xl::mlstm_chunkwise_tc_driver_ok()) return XLSTM_ERR_CUDA;
     void *scratch = nullptr;

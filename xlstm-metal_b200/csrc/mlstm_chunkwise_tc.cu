@@ -115,21 +115,24 @@ mlstm_gate_stats_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int6
     }
 }
 
-// One warp per head.  The chain is sequential but tiny; the warp loads 32 tiles' (G, U) at once and every lane
-// walks them through shuffles, keeping the results of "its" tile for a coalesced write.
+// One warp per (head, segment).  The chain is sequential but tiny; the warp loads 32 tiles' (G, U) at once and
+// every lane walks them through shuffles, keeping the results of "its" tile for a coalesced write.
+// m0_auto: the segment starts from an EMPTY state (C = n = 0): any stabiliser below the first maximum gives the
+// same end state, so the chain starts at the first tile's U (spread 0) instead of -inf.
 __global__ void __launch_bounds__(32)
 mlstm_gate_chain_kernel(const float *__restrict__ m0, double *__restrict__ chain, float *__restrict__ m_out,
-                        int *__restrict__ path, int NCH, int general_only) {
-    const int bh = blockIdx.x, lane = threadIdx.x;
-    double *ch = chain + (size_t)bh * NCH * GC;
+                        int *__restrict__ path, int NCH, int P, int seg_tiles, int general_only, int m0_auto) {
+    const int bhv = blockIdx.x, lane = threadIdx.x;
+    const int tile0 = (bhv % P) * seg_tiles, n = min(seg_tiles, NCH - tile0);
+    double *ch = chain + ((size_t)(bhv / P) * NCH + tile0) * GC;
     // pass 1: the stabiliser chain, and whether every tile's spread x_last - m is bounded
-    double m = m0 ? (double)m0[bh] : 0.0;
+    double m = m0_auto ? ch[1] : (m0 ? (double)m0[bhv] : 0.0);
     bool bounded = !general_only;
-    for (int c0 = 0; c0 < NCH; c0 += 32) {
+    for (int c0 = 0; c0 < n; c0 += 32) {
         const int c = c0 + lane;
-        const double Gl = c < NCH ? ch[(size_t)c * GC + 0] : 0.0, Ul = c < NCH ? ch[(size_t)c * GC + 1] : 0.0;
+        const double Gl = c < n ? ch[(size_t)c * GC + 0] : 0.0, Ul = c < n ? ch[(size_t)c * GC + 1] : 0.0;
         double m_mine = 0.0;
-        const int nb = min(32, NCH - c0);
+        const int nb = min(32, n - c0);
         for (int j = 0; j < nb; ++j) {
             const double Gj = __shfl_sync(0xffffffffu, Gl, j), Uj = __shfl_sync(0xffffffffu, Ul, j);
             const double x_last = fmax(m, Uj);
@@ -137,21 +140,21 @@ mlstm_gate_chain_kernel(const float *__restrict__ m0, double *__restrict__ chain
             if (j == lane) m_mine = m;
             m = Gj + x_last;
         }
-        if (c < NCH) ch[(size_t)c * GC + 2] = m_mine;    // stabiliser carried INTO tile c
+        if (c < n) ch[(size_t)c * GC + 2] = m_mine;    // stabiliser carried INTO tile c
     }
-    if (lane == 0) { m_out[bh] = (float)m; path[bh] = bounded ? 1 : 0; }
+    if (lane == 0) { m_out[bhv] = (float)m; path[bhv] = bounded ? 1 : 0; }
     // pass 2: C is kept in TMEM as C~ = C e^{-rho}: rho absorbs the per-tile decay so that the accumulator is
-    // NOT rescaled every tile; only when -rho would exceed RESCALE_AT is C~ multiplied once (mul).
+    // NOT rescaled every tile; only when -rho would exceed the threshold is C~ multiplied once (mul).
     // General kernel: the multiplication happens BEFORE tile c's update (mul also carries the decay of that
     // tile); bounded-spread kernel: AFTER tile c's update, so that update and read-out of a tile share one
     // frame.  rho_in = frame the read-out of tile c sees, rho_out = frame after tile c's update.
     double rho = 0.0;
-    for (int c0 = 0; c0 < NCH; c0 += 32) {
+    for (int c0 = 0; c0 < n; c0 += 32) {
         const int c = c0 + lane;
         double ld = 0.0;
-        if (c < NCH) ld = ch[(size_t)c * GC + 2] - fmax(ch[(size_t)c * GC + 2], ch[(size_t)c * GC + 1]);   // m - x_last <= 0
+        if (c < n) ld = ch[(size_t)c * GC + 2] - fmax(ch[(size_t)c * GC + 2], ch[(size_t)c * GC + 1]);   // m - x_last <= 0
         double rin = 0.0, rout = 0.0, mul = 1.0;
-        const int nb = min(32, NCH - c0);
+        const int nb = min(32, n - c0);
         for (int j = 0; j < nb; ++j) {
             const double logdec = __shfl_sync(0xffffffffu, ld, j);
             const double r_in = rho;
@@ -167,9 +170,55 @@ mlstm_gate_chain_kernel(const float *__restrict__ m0, double *__restrict__ chain
             }
             if (j == lane) { rin = r_in; rout = r_out; mul = mu; }
         }
-        if (c < NCH) {
+        if (c < n) {
             ch[(size_t)c * GC + 3] = rin; ch[(size_t)c * GC + 4] = rout; ch[(size_t)c * GC + 5] = mul;
         }
+    }
+}
+
+// Segment-parallel prefill: the end state of segment j from an EMPTY state (Cl, nl, ml) and the total log-decay
+// G_j of the segment combine associatively with the state before it,
+//   m' = max(G_j + m, ml);  C' = e^{G_j + m - m'} C + e^{ml - m'} Cl;  n' likewise,
+// so one cheap pass over the P local states yields the true state at the start of every segment (Cs, ns, ms)
+// and the final state.  One CTA per (head, slab of elements); the scalar chain is recomputed per CTA.
+constexpr int COMB_THREADS = 256;
+__global__ void __launch_bounds__(COMB_THREADS)
+mlstm_segment_combine_kernel(const float *__restrict__ C0, const float *__restrict__ n0, const float *__restrict__ m0,
+                             const float *__restrict__ Cl, const float *__restrict__ nl, const float *__restrict__ ml,
+                             const double *__restrict__ chain, float *__restrict__ Cs, float *__restrict__ ns,
+                             float *__restrict__ ms, float *__restrict__ C1, float *__restrict__ n1, float *__restrict__ m1,
+                             int NCH, int P, int seg_tiles, int dqk, int dv) {
+    __shared__ float s_wc[64], s_wl[64];   // weights of the carried and of the local state per segment (P <= 64)
+    const int bh = blockIdx.x;
+    if (threadIdx.x == 0) {
+        double m = C0 ? (double)m0[bh] : 0.0;
+        for (int j = 0; j < P; ++j) {
+            const int tile0 = j * seg_tiles, n = min(seg_tiles, NCH - tile0);
+            double G = 0.0;
+            for (int c = 0; c < n; ++c) G += chain[((size_t)bh * NCH + tile0 + c) * GC + 0];
+            const double mloc = (double)ml[(size_t)bh * P + j];
+            const double mn = fmax(G + m, mloc);
+            if (blockIdx.y == 0) ms[(size_t)bh * P + j] = (float)m;
+            s_wc[j] = (float)exp(G + m - mn);
+            s_wl[j] = (float)exp(mloc - mn);
+            m = mn;
+        }
+        if (blockIdx.y == 0) m1[bh] = (float)m;
+    }
+    __syncthreads();
+    const size_t CE = (size_t)dqk * dv, total = CE + dqk;   // elements of C, then of n
+    for (size_t e = (size_t)blockIdx.y * COMB_THREADS + threadIdx.x; e < total; e += (size_t)gridDim.y * COMB_THREADS) {
+        const bool isC = e < CE;
+        const size_t off = isC ? e : e - CE, per = isC ? CE : (size_t)dqk;
+        const float *src0 = isC ? C0 : n0, *loc = isC ? Cl : nl;
+        float *st = isC ? Cs : ns, *fin = isC ? C1 : n1;
+        float v = C0 ? src0[(size_t)bh * per + off] : 0.f;
+        for (int j = 0; j < P; ++j) {
+            const size_t idx = ((size_t)bh * P + j) * per + off;
+            st[idx] = v;
+            v = s_wc[j] * v + s_wl[j] * loc[idx];
+        }
+        fin[(size_t)bh * per + off] = v;
     }
 }
 
@@ -177,11 +226,11 @@ template <typename T>
 __global__ void __launch_bounds__(GP_THREADS)
 mlstm_gate_write_kernel(const T *__restrict__ ig, const T *__restrict__ fg, int64_t sg_b, int64_t sg_h, int64_t sg_s,
                         const double *__restrict__ chain, const int *__restrict__ path, float *__restrict__ gates,
-                        int NH, int NCH, float qscale, float cap) {
+                        int NH, int NCH, int P, int seg_tiles, float qscale, float cap) {
     const int bh = blockIdx.y, b = bh / NH, hd = bh % NH;
     const int lane = threadIdx.x & 31, c = blockIdx.x * (GP_THREADS / 32) + (threadIdx.x >> 5);
     if (c >= NCH) return;
-    const bool bounded = path[bh] != 0;
+    const bool bounded = path[(size_t)bh * P + c / seg_tiles] != 0;
     double bcum[4], u[4], pmax[4], excl, G, U;
     gate_tile_scan<T>(ig + b * sg_b + hd * sg_h, fg + b * sg_b + hd * sg_h, sg_s, cap, c, lane, bcum, u, pmax, excl, G, U);
     const double *ch = chain + ((size_t)bh * NCH + c) * GC;
@@ -286,11 +335,13 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
     float *s_rs = reinterpret_cast<float *>(smem + SM::INV);   // row sums of P, by tile parity
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int bh = blockIdx.x, b = bh / p.NH, hd = bh % p.NH;
-    if (p.path[bh] != 0) return;   // this head runs in the bounded-spread kernel (CTA-uniform, before any set-up)
+    const int bh = blockIdx.x;     // (batch, head, segment): index of the states and of the path flag
+    if (p.path[bh] != 0) return;   // this segment runs in the bounded-spread kernel (CTA-uniform, before any set-up)
+    const int bhr = bh / p.P, tile0 = (bh % p.P) * p.seg_tiles;   // (batch, head) and first tile of this segment
+    const int b = bhr / p.NH, hd = bhr % p.NH;
     const int col0 = blockIdx.y * DVS;
-    const int NCH = p.NCH;
-    const float *gbase = p.gates + (size_t)bh * NCH * GW;
+    const int NCH = min(p.seg_tiles, p.NCH - tile0);
+    const float *gbase = p.gates + ((size_t)bhr * p.NCH + tile0) * GW;
 
     if (tid == 0) {
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;  // swizzled tiles need a 1024-byte aligned base
@@ -318,7 +369,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         // h tile that the epilogue stages in the V buffer has been read by its TMA stores.
         if (lane == 0) {
             for (int k = 0; k < NCH; ++k) {
-                const int t0 = k * LT;
+                const int t0 = (tile0 + k) * LT;
                 if (k > 0 && !(mbar_wait(&bars[B_UPDDONE], (k - 1) & 1, abort_flag) &&
                                mbar_wait(&bars[B_KREAD], (k - 1) & 1, abort_flag))) break;
                 mbar_expect_tx(&bars[B_KFULL], NBOX * SM::BOX);
@@ -392,7 +443,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
                 if (!mbar_wait(&bars[B_HSTAGED], k & 1, abort_flag)) break;
                 for (int d = 0; d < p.n_h; ++d)
                     for (int bx = 0; bx < 2; ++bx)
-                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, k * LT, hd, b);
+                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, (tile0 + k) * LT, hd, b);
                 tma_store_commit();
                 tma_store_wait_read();            // staging tile consumed: V may be reloaded
                 mbar_arrive(&bars[B_VFREE]);
@@ -632,51 +683,109 @@ bool mlstm_chunkwise_tc_supported(const ChunkwiseParams &p, int dtype) {
     return mlstm_chunkwise_tc_shape_ok(p, dtype) && mlstm_chunkwise_tc_driver_ok();
 }
 
-size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L) {
-    (void)dv; (void)L;
-    const size_t nch = (size_t)(S / LT);
-    // header (status) + gate scalars + hand-over state (n, m) for a tail that runs on the exact path
-    // + one path flag per (batch, head) + the chain scratch of the gate pre-pass
-    size_t bytes = WS_HEADER + (size_t)B * NH * nch * GW * sizeof(float) + (size_t)B * NH * (dqk + 1) * sizeof(float) +
-                   (size_t)B * NH * sizeof(int);
-    bytes = (bytes + 255) & ~(size_t)255;
-    return bytes + (size_t)B * NH * nch * GC * sizeof(double) + 256;
+namespace {
+
+// Layout of the caller-provided scratch.  P > 1 adds the per-segment states of the segment-parallel mode.
+struct WsLayout {
+    size_t gates, tail_n, tail_m, path, chain, seg_C[2], seg_n[2], seg_m[2], total;
+    int P, seg_tiles;
+};
+
+constexpr int SM_COUNT = 148;          // B200
+constexpr int MIN_SEG_TILES = 16;      // a shorter segment is dominated by its prologue (state in) and epilogue (state out)
+
+// Number of segments every sequence is cut into: while the grid of persistent CTAs (one per head and 128 dv
+// columns) fills less than a third of the SMs, cutting the sequence buys parallelism at the price of a second
+// pass (two passes over 1/P of the sequence: a gain from P = 3).
+int plan_segments(int BH, int dv, int nch) {
+    const int ctas = BH * (dv / DVS);
+    int P = SM_COUNT / ctas;
+    if (P > nch / MIN_SEG_TILES) P = nch / MIN_SEG_TILES;
+    if (P > 64) P = 64;
+    return P < 3 ? 1 : P;
 }
 
-namespace {
+WsLayout ws_layout(int B, int NH, int S, int dqk, int dv, int P) {
+    WsLayout w{};
+    const size_t BH = (size_t)B * NH, nch = (size_t)(S / LT);
+    w.P = P;
+    w.seg_tiles = (int)((nch + P - 1) / P);
+    w.P = (int)((nch + w.seg_tiles - 1) / w.seg_tiles);          // no empty segment
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    size_t o = WS_HEADER;                                        // status word
+    w.gates = o;  o = up(o + BH * nch * GW * sizeof(float));     // per-token gate scalars
+    w.tail_n = o; o = up(o + BH * dqk * sizeof(float));          // hand-over state for a tail on the exact path
+    w.tail_m = o; o = up(o + BH * sizeof(float));
+    w.path = o;   o = up(o + BH * w.P * sizeof(int));            // path flag per (head, segment)
+    w.chain = o;  o = up(o + BH * nch * GC * sizeof(double));    // chain scratch of the gate pre-pass
+    if (w.P > 1) {                                               // local / end states and start states of the segments
+        const size_t VH = BH * w.P;
+        for (int set = 0; set < 2; ++set) {
+            w.seg_C[set] = o; o = up(o + VH * dqk * dv * sizeof(float));
+            w.seg_n[set] = o; o = up(o + VH * dqk * sizeof(float));
+            w.seg_m[set] = o; o = up(o + VH * sizeof(float));
+        }
+    }
+    w.total = o + 256;
+    return w;
+}
+
 std::atomic<int> g_general_only{0};
+std::atomic<int> g_segments{-1};       // -1: planned from the grid size; >= 1: forced (tests)
+
+}  // namespace
+
+size_t mlstm_chunkwise_tc_workspace(int B, int NH, int S, int dqk, int dv, int L) {
+    (void)L;
+    const int nch = S / LT;
+    const int forced = g_segments.load();
+    const int P = forced >= 1 ? (forced > nch ? (nch > 0 ? nch : 1) : forced) : plan_segments(B * NH, dv, nch);
+    return ws_layout(B, NH, S, dqk, dv, P).total;
+}
+
+size_t mlstm_chunkwise_tc_workspace_min(int B, int NH, int S, int dqk, int dv) {
+    return ws_layout(B, NH, S, dqk, dv, 1).total;
 }
 
 void mlstm_chunkwise_tc_set_general_only(int on) { g_general_only.store(on ? 1 : 0); }
+void mlstm_chunkwise_tc_set_segments(int segments) { g_segments.store(segments >= 1 ? segments : -1); }
 
 int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspace_bytes, cudaStream_t st) {
     const int s_full = (p.S / LT) * LT;
     const int nch = s_full / LT;
     const int BH = p.B * p.NH;
-    if (!workspace || workspace_bytes < mlstm_chunkwise_tc_workspace(p.B, p.NH, s_full, p.dqk, p.dv, p.L))
-        return XLSTM_ERR_WORKSPACE;
+    if (!workspace) return XLSTM_ERR_WORKSPACE;
+    // the segment-parallel mode if the scratch holds its states, else the plain single pass
+    const int forced = g_segments.load();
+    int P = forced >= 1 ? (forced > nch ? nch : forced) : plan_segments(BH, p.dv, nch);
+    WsLayout w = ws_layout(p.B, p.NH, s_full, p.dqk, p.dv, P);
+    if (workspace_bytes < w.total) {
+        w = ws_layout(p.B, p.NH, s_full, p.dqk, p.dv, 1);
+        if (workspace_bytes < w.total) return XLSTM_ERR_WORKSPACE;
+    }
+    P = w.P;
+    const int seg_tiles = w.seg_tiles;
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     int *status = reinterpret_cast<int *>(ws);
-    float *gates = reinterpret_cast<float *>(ws + WS_HEADER);
-    float *tail_n = gates + (size_t)BH * nch * GW;
-    float *tail_m = tail_n + (size_t)BH * p.dqk;
-    int *path = reinterpret_cast<int *>(tail_m + BH);
-    const size_t chain_off = (static_cast<size_t>(reinterpret_cast<unsigned char *>(path + BH) - ws) + 255) & ~(size_t)255;
-    double *chain = reinterpret_cast<double *>(ws + chain_off);
+    float *gates = reinterpret_cast<float *>(ws + w.gates);
+    float *tail_n = reinterpret_cast<float *>(ws + w.tail_n);
+    float *tail_m = reinterpret_cast<float *>(ws + w.tail_m);
+    int *path = reinterpret_cast<int *>(ws + w.path);
+    double *chain = reinterpret_cast<double *>(ws + w.chain);
+    const size_t CE = (size_t)p.dqk * p.dv;                         // elements of one C
+    // set A: pass 1 local end states (pass 2: end states, unused); set B: the true start state of every segment
+    float *segA_C = reinterpret_cast<float *>(ws + w.seg_C[0]), *segA_n = reinterpret_cast<float *>(ws + w.seg_n[0]);
+    float *segA_m = reinterpret_cast<float *>(ws + w.seg_m[0]);
+    float *segB_C = reinterpret_cast<float *>(ws + w.seg_C[1]), *segB_n = reinterpret_cast<float *>(ws + w.seg_n[1]);
+    float *segB_m = reinterpret_cast<float *>(ws + w.seg_m[1]);
     const bool tail = s_full < p.S;
     if (tail && p.n_peer) return XLSTM_ERR_UNSUPPORTED;   // the exact tail path writes the local h only
     if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return XLSTM_ERR_CUDA;
 
-    {
-        const __nv_bfloat16 *ig = static_cast<const __nv_bfloat16 *>(p.ig), *fg = static_cast<const __nv_bfloat16 *>(p.fg);
-        const dim3 tg((nch + GP_THREADS / 32 - 1) / (GP_THREADS / 32), BH);
-        mlstm_gate_stats_kernel<__nv_bfloat16><<<tg, GP_THREADS, 0, st>>>(ig, fg, p.sg[0], p.sg[1], p.sg[2], chain, p.NH, nch,
-                                                                          p.gate_cap);
-        mlstm_gate_chain_kernel<<<BH, 32, 0, st>>>(p.C0 ? p.m0 : nullptr, chain, tail ? tail_m : p.m1, path, nch,
-                                                   g_general_only.load());
-        mlstm_gate_write_kernel<__nv_bfloat16><<<tg, GP_THREADS, 0, st>>>(ig, fg, p.sg[0], p.sg[1], p.sg[2], chain, path, gates,
-                                                                          p.NH, nch, p.qscale, p.gate_cap);
-    }
+    const __nv_bfloat16 *ig = static_cast<const __nv_bfloat16 *>(p.ig), *fg = static_cast<const __nv_bfloat16 *>(p.fg);
+    const dim3 tg((nch + GP_THREADS / 32 - 1) / (GP_THREADS / 32), BH);
+    mlstm_gate_stats_kernel<__nv_bfloat16><<<tg, GP_THREADS, 0, st>>>(ig, fg, p.sg[0], p.sg[1], p.sg[2], chain, p.NH, nch,
+                                                                      p.gate_cap);
     if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
 
     TcParams tp{};
@@ -684,35 +793,62 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
         !make_tmap_bf16_4d(&tp.tk, p.k, p.dqk, s_full, p.NH, p.B, p.sk[2], p.sk[1], p.sk[0], LT) ||
         !make_tmap_bf16_4d(&tp.tv, p.v, p.dv, s_full, p.NH, p.B, p.sv[2], p.sv[1], p.sv[0], LT))
         return XLSTM_ERR_UNSUPPORTED;
-    tp.gates = gates;
-    tp.C0 = p.C0; tp.n0 = p.n0;
-    tp.n_h = 1 + p.n_peer;
-    for (int i = 0; i < tp.n_h; ++i)
+    for (int i = 0; i < 1 + p.n_peer; ++i)
         if (!make_tmap_bf16_4d(&tp.th[i], i == 0 ? p.h : p.h_peer[i - 1], p.dv, s_full, p.NH, p.B, p.sh[2], p.sh[1], p.sh[0], LT))
             return XLSTM_ERR_UNSUPPORTED;
-    tp.C1 = p.C1; tp.n1 = tail ? tail_n : p.n1;
+    tp.gates = gates;
     tp.NH = p.NH; tp.dv = p.dv; tp.NCH = nch; tp.eps = p.eps; tp.log2_qscale = log2f(p.qscale); tp.status = status;
-    tp.path = path; tp.h = p.h;
+    tp.path = path; tp.h = p.h; tp.P = P; tp.seg_tiles = seg_tiles;
     for (int d = 0; d < 3; ++d) tp.sh[d] = p.sh[d];
-    dim3 grid(BH, p.dv / DVS);
-    // Two launches over the same grid: every CTA looks at its head's path flag (written by the pre-pass) and
-    // returns at once if the head belongs to the other kernel, so the choice needs no host round trip.
-    const int rc = mlstm_chunkwise_tc_fast_launch(tp, grid, p.dqk, st);
-    if (rc != XLSTM_OK) return rc;
-    cudaError_t e;
-    if (p.dqk == 256) {
-        auto kern = mlstm_chunkwise_tc_kernel<256>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<256>::TOTAL) != cudaSuccess)
-            return XLSTM_ERR_CUDA;
-        kern<<<grid, THREADS, Smem<256>::TOTAL, st>>>(tp);
+    const dim3 grid(BH * P, p.dv / DVS);
+
+    // one forward over all (head, segment) pairs: chain + per-token scalars of the gate pre-pass, then the two
+    // tensor-core kernels.  Two launches over the same grid: every CTA looks at its path flag (written by the
+    // pre-pass) and returns at once if it belongs to the other kernel, so the choice needs no host round trip.
+    auto forward = [&](const float *m0v, int m0_auto, float *m_out) -> int {
+        mlstm_gate_chain_kernel<<<BH * P, 32, 0, st>>>(m0v, chain, m_out, path, nch, P, seg_tiles, g_general_only.load(),
+                                                       m0_auto);
+        mlstm_gate_write_kernel<__nv_bfloat16><<<tg, GP_THREADS, 0, st>>>(ig, fg, p.sg[0], p.sg[1], p.sg[2], chain, path, gates,
+                                                                          p.NH, nch, P, seg_tiles, p.qscale, p.gate_cap);
+        if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
+        const int rc = mlstm_chunkwise_tc_fast_launch(tp, grid, p.dqk, st);
+        if (rc != XLSTM_OK) return rc;
+        if (p.dqk == 256) {
+            auto kern = mlstm_chunkwise_tc_kernel<256>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<256>::TOTAL) != cudaSuccess)
+                return XLSTM_ERR_CUDA;
+            kern<<<grid, THREADS, Smem<256>::TOTAL, st>>>(tp);
+        } else {
+            auto kern = mlstm_chunkwise_tc_kernel<128>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<128>::TOTAL) != cudaSuccess)
+                return XLSTM_ERR_CUDA;
+            kern<<<grid, THREADS, Smem<128>::TOTAL, st>>>(tp);
+        }
+        return cudaGetLastError() == cudaSuccess ? XLSTM_OK : XLSTM_ERR_CUDA;
+    };
+
+    float *n_final = tail ? tail_n : p.n1, *m_final = tail ? tail_m : p.m1;
+    if (P == 1) {
+        tp.C0 = p.C0; tp.n0 = p.n0; tp.C1 = p.C1; tp.n1 = n_final; tp.n_h = 1 + p.n_peer;
+        const int rc = forward(p.C0 ? p.m0 : nullptr, 0, m_final);
+        if (rc != XLSTM_OK) return rc;
     } else {
-        auto kern = mlstm_chunkwise_tc_kernel<128>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem<128>::TOTAL) != cudaSuccess)
-            return XLSTM_ERR_CUDA;
-        kern<<<grid, THREADS, Smem<128>::TOTAL, st>>>(tp);
+        // pass 1: every segment from an empty state -> its local end state (h is written too and overwritten by pass 2;
+        // nothing goes to the peers yet)
+        tp.C0 = nullptr; tp.n0 = nullptr; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = 1;
+        int rc = forward(nullptr, 1, segA_m);
+        if (rc != XLSTM_OK) return rc;
+        // the true state at the start of every segment, and the final state
+        const int slabs = (int)((CE + p.dqk + 64 * COMB_THREADS - 1) / (64 * COMB_THREADS));
+        mlstm_segment_combine_kernel<<<dim3(BH, slabs), COMB_THREADS, 0, st>>>(
+            p.C0, p.n0, p.C0 ? p.m0 : nullptr, segA_C, segA_n, segA_m, chain, segB_C, segB_n, segB_m, p.C1, n_final,
+            m_final, nch, P, seg_tiles, p.dqk, p.dv);
+        if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
+        // pass 2: every segment from its true start state
+        tp.C0 = segB_C; tp.n0 = segB_n; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = 1 + p.n_peer;
+        rc = forward(segB_m, 0, segA_m);
+        if (rc != XLSTM_OK) return rc;
     }
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return XLSTM_ERR_CUDA;
     if (!tail) return XLSTM_OK;
 
     // S mod 128 tail on the exact path, continuing from (C1, tail_n, tail_m).  C is handed over in

@@ -28,7 +28,9 @@ struct TcParams {
     int NH, dv, NCH;
     float eps, log2_qscale;
     int *status;
-    const int *path;               // [B*NH] 1: this head's gates fit the bounded-spread kernel, 0: general kernel
+    const int *path;               // [B*NH*P] 1: this (head, segment) fits the bounded-spread kernel, 0: general kernel
+    int P, seg_tiles;              // the sequence of every head is cut into P segments of seg_tiles tiles (P = 1: no cut);
+                                   // blockIdx.x = (batch * NH + head) * P + segment; C0, n0, C1, n1 and path are per segment
     void *h;                       // h of this GPU as a plain pointer with its element strides (batch, head, token)
     int64_t sh[3];
 };

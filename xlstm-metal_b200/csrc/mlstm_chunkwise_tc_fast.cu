@@ -153,8 +153,8 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
     constexpr int NHALF = DQK / 128;
     constexpr int F_UPDLAST = (NHALF == 2) ? F_UPDB : F_UPDA;
     extern __shared__ __align__(1024) unsigned char smem[];
-    const int bh = blockIdx.x;
-    if (p.path[bh] != 1) return;   // this head's gates need the general kernel (CTA-uniform, before any set-up)
+    const int bh = blockIdx.x;     // (batch, head, segment): index of the states and of the path flag
+    if (p.path[bh] != 1) return;   // these gates need the general kernel (CTA-uniform, before any set-up)
 
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + SM::BARS);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + SM::MISC);
@@ -165,10 +165,11 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
     float *s_a = s_rs + LT;                                          // a_s of the current tile
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = bh / p.NH, hd = bh % p.NH;
+    const int bhr = bh / p.P, tile0 = (bh % p.P) * p.seg_tiles;   // (batch, head) and first tile of this segment
+    const int b = bhr / p.NH, hd = bhr % p.NH;
     const int col0 = blockIdx.y * DVS;
-    const int NCH = p.NCH;
-    const float *gbase = p.gates + (size_t)bh * NCH * GW;
+    const int NCH = min(p.seg_tiles, p.NCH - tile0);
+    const float *gbase = p.gates + ((size_t)bhr * p.NCH + tile0) * GW;
 
     if (tid == 0) {
         *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;  // swizzled tiles need a 1024-byte aligned base
@@ -200,13 +201,13 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
         // follows the read-out) and the q . n pass, K after the update and the normaliser sums, V after P V.
         if (lane == 0) {
             for (int k = 0; k < NCH; ++k) {
-                const int t0 = k * LT;
+                const int t0 = (tile0 + k) * LT;
                 const uint32_t pp = (k - 1) & 1;
                 // A load that misses L2 takes 2-3 k clocks from issue to completion (DRAM latency, whatever its
                 // size), more than the window in which a single-buffered tile is free: the boxes of the tile after
                 // the next one are pulled into L2 here, a tile and a half before their loads are issued.
                 if (k + PREFETCH_AHEAD < NCH) {
-                    const int tp = (k + PREFETCH_AHEAD) * LT;
+                    const int tp = (tile0 + k + PREFETCH_AHEAD) * LT;
                     for (int q = 0; q < NBOX; ++q) { tma_prefetch_4d(&p.tq, q * 64, tp, hd, b); tma_prefetch_4d(&p.tk, q * 64, tp, hd, b); }
                     for (int q = 0; q < 2; ++q) tma_prefetch_4d(&p.tv, col0 + q * 64, tp, hd, b);
                 }
@@ -290,7 +291,7 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
                 if (!mbar_wait(&bars[F_HSTAGED], k & 1, abort_flag)) break;
                 for (int d = 0; d < p.n_h; ++d)
                     for (int bx = 0; bx < 2; ++bx)
-                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, k * LT, hd, b);
+                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, (tile0 + k) * LT, hd, b);
                 tma_store_commit();
                 tma_store_wait_read();            // staging tile consumed: V may be reloaded
                 mbar_arrive(&bars[F_VFREE]);

@@ -25,6 +25,7 @@ _SIGNATURES = {
                                             ctypes.POINTER(c_void_p), c_int, c_void_p]),
     "xlstm_mlstm_chunkwise_workspace_bytes": (c_size_t, [c_int] * 7),
     "xlstm_mlstm_chunkwise_set_general_only": (c_int, [c_int]),
+    "xlstm_mlstm_chunkwise_set_segments": (c_int, [c_int]),
     "xlstm_mlstm_chunkwise_status": (c_int, [c_void_p, c_void_p]),
     "xlstm_slstm_recurrent_status": (c_int, [c_void_p]),
     "xlstm_mlstm_chunkwise_fwd_static": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6

@@ -100,6 +100,11 @@ def chunkwise_general_only(on: bool) -> None:
     _lib.load().xlstm_mlstm_chunkwise_set_general_only(1 if on else 0)
 
 
+def chunkwise_segments(segments: Optional[int]) -> None:
+    """Force the number of segments of the segment-parallel prefill (``None`` or < 1: chosen from the grid size)."""
+    _lib.load().xlstm_mlstm_chunkwise_set_segments(int(segments) if segments else -1)
+
+
 def chunkwise_status(workspace: Optional[torch.Tensor] = None) -> None:
     """Raise ``XlstmCudaError`` if a bounded device-side wait of the last chunkwise forward that used
     ``workspace`` gave up (``None``: the library's built-in block).  Synchronises the current stream."""
