@@ -3,6 +3,9 @@
 Tolerances (max|a-b| / max|b|): fp32 1e-4 on h, C, n and 1e-4 absolute on m;
 bf16 activations with fp32 state 2e-2.
 """
+import sys
+from pathlib import Path
+
 import numpy as np
 import pytest
 import torch
@@ -459,3 +462,27 @@ def test_chunkwise_segment_parallel_equals_single_pass(ops, general):
     finally:
         ops.chunkwise_segments(None)
         ops.chunkwise_general_only(False)
+
+
+def test_bounded_wait_gives_up_and_status_queries_report_ok(ops):
+    """Device-side time-outs without hanging anything: (a) the bounded mbarrier wait of the tensor-core kernels,
+    built with a tiny poll limit in a test-only kernel, on a barrier nobody arrives at - it must return false,
+    raise the abort flag (which releases every other role) and let the kernel end normally; (b) after real
+    forwards the status queries of the C ABI report no time-out."""
+    import ctypes
+    sys_path = Path(__file__).resolve().parent / "helpers"
+    sys.path.insert(0, str(sys_path))
+    from build_helpers import build
+    lib = ctypes.CDLL(str(build()))
+    out = (ctypes.c_int * 3)()
+    assert lib.timeout_probe_run(out) == 0
+    assert list(out) == [0, 0, 1]
+    rng = np.random.default_rng(2)
+    B, NH, S, dqk, dv = 1, 1, 256, 128, 128
+    q, k = (dev(rng.standard_normal((B, NH, S, dqk)).astype(np.float32), torch.bfloat16) for _ in range(2))
+    v = dev(rng.standard_normal((B, NH, S, dv)).astype(np.float32), torch.bfloat16)
+    i, f = (dev(a, torch.bfloat16) for a in gates(rng, (B, NH, S)))
+    ws = torch.empty(ops.chunkwise_workspace_bytes(B, NH, S, dqk, dv, 64, torch.bfloat16), dtype=torch.uint8, device="cuda")
+    ops.mlstm_chunkwise(q, k, v, i, f, workspace=ws)
+    ops.chunkwise_status(ws)            # raises on XLSTM_ERR_TIMEOUT
+    ops.slstm_recurrent_status()

@@ -184,3 +184,41 @@ def test_single_token_fused_block_path_bf16(tiny_model):
                 assert relerr(host(y1), host(y2)) < 2e-2
             for a, b in zip(s1, s2):
                 assert relerr(host(a), host(b)) < 2e-2
+
+
+def test_head_sharded_blocks_equal_the_unsharded_block(tiny_model, golden):
+    """Two head shards of one block, run one after the other on this GPU with the all-gather replaced by a
+    concatenation: gated head outputs, out-projection and states must equal the unsharded block's (the
+    collective itself is covered by the gloo test on CPU and the two-GPU test)."""
+    import copy
+    model, _ = tiny_model
+    g = golden("model_tiny_fp32")
+    blk = model.blocks[0]
+    x = torch.from_numpy(g["block0_in"]).cuda()
+    NH = blk.mlstm_cell.num_heads
+    shards = []
+    for rank in range(NH):
+        s = copy.deepcopy(blk)
+        s.shard_heads(rank, NH)
+        shards.append(s.cuda())
+    with torch.inference_mode():
+        xn = blk.norm_mlstm(x)
+        want, st = blk.mlstm_cell(xn, None)
+        gated, states = [], []
+        for s in shards:
+            cell = s.mlstm_cell
+            q, k, v, i, f, _ = cell._project(xn)
+            h, st_local = cell.parallel_kernel(q[:, :, :64], k[:, :, :64], v[:, :, :64], i[:, :, :64], f[:, :, :64], None)
+            h2, st_local = cell.recurrent_kernel(q[:, :, 64:], k[:, :, 64:], v[:, :, 64:], i[:, :, 64:], f[:, :, 64:], st_local)
+            gated.append(cell.output_cell.gate(torch.cat([h, h2], 2), cell.output_cell.ogate_proj(xn)))
+            states.append(st_local)
+        got = blk.mlstm_cell.output_cell.out_proj(torch.cat(gated, dim=-1))
+    assert relerr(host(got), host(want)) < TOL
+    for j in range(3):
+        assert relerr(host(torch.cat([s_[j] for s_ in states], 1)), host(st[j])) < TOL
+    # a one-rank "shard" goes through the sharded forward path (gather is the identity) and equals the block
+    solo = copy.deepcopy(blk)
+    solo.shard_heads(0, 1)
+    with torch.inference_mode():
+        y1, _ = solo.cuda()(x, None)
+    assert relerr(host(y1), g["block0_out"]) < TOL

@@ -42,6 +42,11 @@ def _worker(rank, world, port, tmp):
     lo, hi = parallel.head_range(NH, world, rank)
     ok = torch.allclose(y, y_ref, rtol=1e-5, atol=1e-5) and torch.allclose(st_local[0], st_full[0][:, lo:hi], atol=1e-6)
     ok = ok and st_local[2].shape == (B, NH // world)
+    # gather along the feature dimension (gated head outputs before the replicated out-projection)
+    feats = torch.arange(B * S * NH * dv, dtype=torch.float32).reshape(B, S, NH * dv)
+    per = NH * dv // world
+    got = parallel.all_gather_features(feats[..., rank * per:(rank + 1) * per])
+    ok = ok and torch.equal(got, feats)
     Path(tmp, f"ok{rank}").write_text("1" if ok else "0")
     dist.destroy_process_group()
 

@@ -90,3 +90,56 @@ def test_missing_shards_raise(tmp_path):
     from xlstm_cuda.utils import load_safetensor_shards
     with pytest.raises(FileNotFoundError):
         load_safetensor_shards(str(tmp_path))
+
+
+def test_infer_config_from_safetensors_reads_shapes_of_all_shards(tmp_path):
+    """Follows xlstm_metal/torch_native/utils/infer_config_from_safetensors.py:30-103 on a two-shard checkpoint
+    whose block-0 tensors sit in both shards; no config.json is consulted."""
+    from xlstm_cuda.utils import infer_config_from_safetensors
+    src, tensors, ckpt = _checkpoint(tmp_path, ["mlstm", "mlstm"])
+    (ckpt / "config.json").unlink()
+    cfg = infer_config_from_safetensors(str(ckpt))
+    assert cfg["embedding_dim"] == TINY["embedding_dim"] and cfg["vocab_size"] == TINY["vocab_size"]
+    assert cfg["num_blocks"] == 2 and cfg["num_heads"] == TINY["num_heads"]
+    assert cfg["qk_dim_factor"] == pytest.approx(TINY["qk_dim_factor"]) and cfg["v_dim_factor"] == 1.0
+    assert cfg["ffn_proj_factor"] * TINY["embedding_dim"] == src.blocks[0].ffn_hidden_dim
+    assert cfg["gate_soft_cap"] == 15.0 and cfg["output_logit_soft_cap"] == 30.0 and cfg["chunk_size"] == 64
+    assert cfg["use_bias"] is True and cfg["norm_eps"] == 1e-6
+    with pytest.raises(FileNotFoundError):
+        infer_config_from_safetensors(str(tmp_path))
+    # a required tensor missing from the index -> ValueError, as in the reference
+    idx = json.loads((ckpt / "model.safetensors.index.json").read_text())
+    del idx["weight_map"]["lm_head.weight"]
+    (ckpt / "model.safetensors.index.json").write_text(json.dumps(idx))
+    with pytest.raises(ValueError):
+        infer_config_from_safetensors(str(ckpt))
+
+
+def test_head_sharded_model_loads_its_row_slices(tmp_path):
+    """head_shard=(rank, world): every mLSTM layer keeps the rows of q/k/v/igate/fgate/ogate and of the per-head
+    norm weight that belong to its heads (key map: xlstm_metal/torch_native/blocks/mlstm/mlstm_block.py:215-231);
+    everything else, the out-projection included, is the full tensor."""
+    from xlstm_cuda.models import WiredxLSTM
+    src, tensors, ckpt = _checkpoint(tmp_path, ["mlstm", "slstm", "mlstm"])
+    NH = TINY["num_heads"]
+    full = dict(src.named_parameters())
+    for rank in range(NH):
+        m = WiredxLSTM.from_pretrained(ckpt, load_weights=True, device="cpu", head_shard=(rank, NH))
+        cell = m.blocks[0].mlstm_cell
+        dqk, dv = cell.qk_dim_per_head, cell.v_dim_per_head
+        assert cell.num_heads == 1 and cell.projection_cell.q_proj.out_features == dqk
+        rows = {"q_proj.weight": dqk, "k_proj.weight": dqk, "v_proj.weight": dv, "igate_proj.weight": 1, "igate_proj.bias": 1,
+                "fgate_proj.weight": 1, "fgate_proj.bias": 1}
+        for name, per in rows.items():
+            want = full[f"blocks.0.mlstm_cell.projection_cell.{name}"][rank * per:(rank + 1) * per]
+            assert torch.equal(dict(m.named_parameters())[f"blocks.0.mlstm_cell.projection_cell.{name}"], want), name
+        mine = dict(m.named_parameters())
+        for name in ("ogate_proj.weight", "norm.weight"):
+            want = full[f"blocks.2.mlstm_cell.output_cell.{name}"][rank * dv:(rank + 1) * dv]
+            assert torch.equal(mine[f"blocks.2.mlstm_cell.output_cell.{name}"], want), name
+        for name in ("blocks.0.mlstm_cell.output_cell.out_proj.weight", "blocks.0.ffn_proj_down.weight", "lm_head.weight",
+                     "blocks.0.norm_mlstm.weight"):
+            assert torch.equal(mine[name], full[name]), name
+        assert not m.blocks[0]._token_step_ok(torch.zeros(1, 1, TINY["embedding_dim"], dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        WiredxLSTM.from_pretrained(ckpt, load_weights=False, device="cpu", head_shard=(0, 3))

@@ -134,11 +134,13 @@ class mLSTMOutputCell(nn.Module):
     def forward(self, h: torch.Tensor, x_orig: torch.Tensor) -> torch.Tensor:
         return self.forward_gated(h, self.ogate_proj(x_orig))
 
+    def gate(self, h: torch.Tensor, o_preact: torch.Tensor) -> torch.Tensor:
+        """norm(h) * sigmoid(ogate) in one pass over h [B,NH,S,dv] -> [B,S,NH*dv]; no soft-cap on the output gate."""
+        return ops.mlstm_output_gate(h, o_preact, self.norm.weight, self.norm.eps)
+
     def forward_gated(self, h: torch.Tensor, o_preact: torch.Tensor) -> torch.Tensor:
         """``o_preact`` = ``ogate_proj(x)`` computed by the caller (a column block of a fused GEMM)."""
-        # norm(h) * sigmoid(ogate) in one pass over h [B,NH,S,dv]; no soft-cap on the output gate
-        gated = ops.mlstm_output_gate(h, o_preact, self.norm.weight, self.norm.eps)
-        return self.out_proj(gated)
+        return self.out_proj(self.gate(h, o_preact))
 
 
 class mLSTMNeuron(nn.Module):
@@ -166,6 +168,56 @@ class mLSTMNeuron(nn.Module):
         self.recurrent_kernel = mLSTMRecurrentKernelCell(num_heads, qk_dim_per_head, v_dim_per_head, eps,
                                                          compute_dtype, state_dtype)
         self.output_cell = mLSTMOutputCell(input_size, num_heads, v_dim_per_head, use_bias=use_bias, eps=eps)
+
+    # ---- heads sharded over the ranks of a process group -------------------------------------------
+    def shard_heads(self, rank: int, world: int, group=None) -> None:
+        """Keep only this rank's heads ``[rank*NH/world, (rank+1)*NH/world)``: the row slices of the q, k, v,
+        igate, fgate and ogate projections and of the per-head norm weight, and the heads' (C, n, m).  Heads
+        never interact inside the cell and the norm is per head, so everything up to ``norm(h) * sigmoid(o)``
+        is local; ``forward`` then all-gathers the gated ``[B, S, NH/world * dv]`` slices (one collective)
+        and applies the replicated out-projection.  Call before loading weights: ``weight_row_slice`` tells
+        the loader which rows of a full checkpoint tensor belong here."""
+        from ..parallel import head_range
+        if getattr(self, "_shard", None) is not None:
+            raise RuntimeError("heads are already sharded")
+        lo, hi = head_range(self.num_heads, world, rank)
+        nh_total, dqk, dv = self.num_heads, self.qk_dim_per_head, self.v_dim_per_head
+        pc, oc = self.projection_cell, self.output_cell
+
+        def keep_rows(lin: nn.Linear, per_head: int) -> None:
+            lin.weight = nn.Parameter(lin.weight.data[lo * per_head:hi * per_head].clone(), requires_grad=lin.weight.requires_grad)
+            if lin.bias is not None:
+                lin.bias = nn.Parameter(lin.bias.data[lo * per_head:hi * per_head].clone(), requires_grad=lin.bias.requires_grad)
+            lin.out_features = (hi - lo) * per_head
+
+        for lin, per in ((pc.q_proj, dqk), (pc.k_proj, dqk), (pc.v_proj, dv), (pc.igate_proj, 1), (pc.fgate_proj, 1),
+                         (oc.ogate_proj, dv)):
+            keep_rows(lin, per)
+        if oc.norm.weight is not None:
+            oc.norm.weight = nn.Parameter(oc.norm.weight.data[lo * dv:hi * dv].clone(), requires_grad=oc.norm.weight.requires_grad)
+        for mod in (self, pc, oc, oc.norm, self.parallel_kernel, self.recurrent_kernel):
+            mod.num_heads = hi - lo
+        self._fused = None
+        self._shard = (rank, world, group, nh_total, lo, hi)
+
+    def weight_row_slice(self, path: str) -> Optional[slice]:
+        """Rows of the FULL tensor that the (sharded) parameter ``path`` (relative to this neuron) holds."""
+        shard = getattr(self, "_shard", None)
+        if shard is None:
+            return None
+        lo, hi = shard[4], shard[5]
+        per = {"projection_cell.q_proj": self.qk_dim_per_head, "projection_cell.k_proj": self.qk_dim_per_head,
+               "projection_cell.v_proj": self.v_dim_per_head, "projection_cell.igate_proj": 1,
+               "projection_cell.fgate_proj": 1, "output_cell.ogate_proj": self.v_dim_per_head,
+               "output_cell.norm": self.v_dim_per_head}.get(path.rsplit(".", 1)[0])
+        return None if per is None else slice(lo * per, hi * per)
+
+    def _gather_gated(self, gated: torch.Tensor) -> torch.Tensor:
+        shard = getattr(self, "_shard", None)
+        if shard is None or shard[1] == 1:
+            return gated
+        from ..parallel import all_gather_features
+        return all_gather_features(gated, shard[2])
 
     @property
     def state_size(self) -> Tuple[int, int, int]:
@@ -249,9 +301,9 @@ class mLSTMNeuron(nn.Module):
                                                f_preact[:, :, sl], cur, gate_cap=cap)
             pieces.append(h_seq)
         h = pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=2)
-        if o_preact is None:
-            return self.output_cell(h, x), cur
-        return self.output_cell.forward_gated(h, o_preact), cur
+        oc = self.output_cell
+        gated = oc.gate(h, oc.ogate_proj(x) if o_preact is None else o_preact)   # this rank's heads
+        return oc.out_proj(self._gather_gated(gated)), cur
 
     def get_config(self) -> dict:
         return {"input_size": self.input_size, "num_heads": self.num_heads, "qk_dim_per_head": self.qk_dim_per_head,
@@ -321,7 +373,17 @@ class mLSTMBlock(nn.Module):
         x3 = ops.linear_token(self.ffn_proj_down.weight, act, bias=self.ffn_proj_down.bias, residual=x1)
         return x3.view_as(x), rk._cast_state(new_state)
 
+    def shard_heads(self, rank: int, world: int, group=None) -> None:
+        """Head-sharded mLSTM layer (see ``mLSTMNeuron.shard_heads``); norms and the FFN stay replicated."""
+        self.mlstm_cell.shard_heads(rank, world, group)
+
+    def weight_row_slice(self, path: str) -> Optional[slice]:
+        prefix = "mlstm_cell."
+        return self.mlstm_cell.weight_row_slice(path[len(prefix):]) if path.startswith(prefix) else None
+
     def _token_step_ok(self, x: torch.Tensor) -> bool:
+        if getattr(self.mlstm_cell, "_shard", None) is not None:
+            return False   # the six-launch single-token path has no gather step
         return (x.shape[1] == 1 and x.shape[0] <= ops.LINEAR_TOKEN_MAX_ROWS and x.dtype == torch.bfloat16 and
                 self.mlstm_cell._fused_weights() is not None and self._fused_ffn() is not None and
                 self.mlstm_cell.compute_dtype == torch.bfloat16)

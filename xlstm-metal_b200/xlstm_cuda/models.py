@@ -21,8 +21,13 @@ from .wiring import AutoWiring, create_auto_wiring
 class WiredxLSTM(nn.Module):
     def __init__(self, wiring: AutoWiring, load_weights: bool = False, model_dir: Optional[Union[str, Path]] = None,
                  compute_dtype: torch.dtype = torch.float32, state_dtype: torch.dtype = torch.float32,
-                 norm_reduce_force_float32: bool = True, device: Optional[torch.device] = None):
+                 norm_reduce_force_float32: bool = True, device: Optional[torch.device] = None,
+                 head_shard: Optional[Tuple[int, int]] = None, head_shard_group=None):
+        """``head_shard=(rank, world)`` (not in the reference, which is single-device): every mLSTM layer keeps only
+        this rank's heads (column slices of q/k/v/igate/fgate/ogate, its heads' norm weights and states) and
+        all-gathers the gated head outputs before its replicated out-projection; everything else is replicated."""
         super().__init__()
+        self.head_shard, self.head_shard_group = head_shard, head_shard_group
         self.wiring = wiring
         self.config = wiring.config
         self.model_dir = Path(model_dir) if model_dir else wiring.model_dir
@@ -52,6 +57,8 @@ class WiredxLSTM(nn.Module):
                                                      norm_reduction_force_float32=self.norm_reduce_force_float32)
             # every parameter, norm weights included, in the compute dtype: a stray fp32 weight would
             # promote the activations and break the next Linear
+            if self.head_shard is not None and hasattr(cell, "shard_heads"):
+                cell.shard_heads(self.head_shard[0], self.head_shard[1], self.head_shard_group)
             self.blocks.append(cell.to(device=dev, dtype=dt))
         self.out_norm = RMSNormCell(dims=d).to(device=dev, dtype=dt) if st["has_out_norm"] else None
         self.lm_head = nn.Linear(d, vocab, bias=False, device=dev, dtype=dt) if st["has_lm_head"] else None
@@ -93,10 +100,11 @@ class WiredxLSTM(nn.Module):
         self._load_weights_from_dict(load_safetensor_shards(str(self.model_dir)))
 
     def _load_weights_from_dict(self, weights: Dict[str, torch.Tensor]) -> None:
-        def assign(param: torch.Tensor, key: str) -> None:
+        def assign(param: torch.Tensor, key: str, rows: Optional[slice] = None) -> None:
             if key in weights:
+                w = weights[key] if rows is None else weights[key][rows]   # a head-sharded layer takes its row slice
                 with torch.no_grad():
-                    param.copy_(weights[key].to(device=param.device, dtype=param.dtype))
+                    param.copy_(w.to(device=param.device, dtype=param.dtype))
 
         if self.embedding is not None:
             assign(self.embedding.weight, "backbone.embeddings.weight")
@@ -104,7 +112,7 @@ class WiredxLSTM(nn.Module):
             params = dict(block.named_parameters())
             for path, key in block.get_weight_keys().items():
                 if path in params:
-                    assign(params[path], key)
+                    assign(params[path], key, block.weight_row_slice(path) if hasattr(block, "weight_row_slice") else None)
         if self.out_norm is not None:
             assign(self.out_norm.weight, "backbone.out_norm.weight")
         if self.lm_head is not None:

@@ -53,6 +53,19 @@ def all_gather_heads(h_local: torch.Tensor, group: Optional[dist.ProcessGroup] =
     return gathered.view(world, B, nh, S, dv).permute(1, 0, 2, 3, 4).reshape(B, world * nh, S, dv)
 
 
+def all_gather_features(x_local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """``[..., F/G]`` on every rank -> ``[..., F]`` on every rank (rank r's slice is block r of the last
+    dimension): the gather of the gated per-head outputs before the replicated out-projection."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return x_local
+    x_local = x_local.contiguous()
+    shape = tuple(x_local.shape)
+    gathered = torch.empty((world * shape[0],) + shape[1:], dtype=x_local.dtype, device=x_local.device)  # rank-major
+    dist.all_gather_into_tensor(gathered, x_local, group=group)
+    return torch.cat(list(gathered.view((world,) + shape).unbind(0)), dim=-1)
+
+
 def head_sharded_prefill(cell: Callable, q, k, v, i, f, state=None, out_proj: Optional[torch.Tensor] = None,
                          group: Optional[dist.ProcessGroup] = None):
     """Run ``cell(q, k, v, i, f, state) -> (h, state)`` on this rank's heads, all-gather h, and apply

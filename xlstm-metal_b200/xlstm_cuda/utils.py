@@ -3,6 +3,7 @@
 ``load_config``      xlstm_metal/torch_native/utils/config_loader.py:23-72 (derived dims, defaults)
 ``resolve_dtype``    xlstm_metal/torch_native/utils/dtype_utils.py:9-31
 ``load_safetensor_shards``  xlstm_metal/torch_native/utils/safetensors_torch_loader.py:11-45
+``infer_config_from_safetensors``  xlstm_metal/torch_native/utils/infer_config_from_safetensors.py:30-103
 ``write_model_dir``  new: writes ``config.json`` plus a keys-only ``model.safetensors.index.json`` so a
                      random-init model can go through the unchanged wiring / ``from_pretrained`` API
                      (the wiring reads block types from that index: wiring/auto_wiring.py:37-70).
@@ -66,6 +67,57 @@ def load_safetensor_shards(model_dir: str) -> Dict[str, torch.Tensor]:
     return out
 
 
+def infer_config_from_safetensors(model_dir: str) -> Dict[str, Any]:
+    """Model configuration read off the tensor shapes of a checkpoint (no ``config.json`` needed).
+
+    Same required tensors, consistency checks, error types and returned keys as the reference function.  Two
+    differences, both additive: shapes are read from the shard headers of EVERY shard (the reference loads the
+    tensors of the first shard only, so a block-0 tensor stored in a later shard is "not found"), and the head
+    count comes from the input-gate bias (one entry per head) instead of the constant 8, which it falls back to."""
+    from safetensors import safe_open
+    root = Path(model_dir)
+    index_path = root / "model.safetensors.index.json"
+    if not index_path.exists():
+        raise FileNotFoundError(f"Safetensors index not found: {index_path}")
+    index = json.loads(index_path.read_text())
+    weight_map = index["weight_map"]
+    shapes: Dict[str, tuple] = {}
+    for shard in sorted(set(weight_map.values())):
+        if (root / shard).exists():
+            with safe_open(str(root / shard), framework="pt", device="cpu") as f:
+                for name in f.keys():
+                    shapes[name] = tuple(f.get_slice(name).get_shape())
+
+    def shape_of(name: str) -> tuple:
+        if name in weight_map and name in shapes:
+            return shapes[name]
+        meta = index.get("metadata", {}).get(name, {}) if isinstance(index.get("metadata"), dict) else {}
+        if isinstance(meta, dict) and meta.get("shape"):
+            return tuple(meta["shape"])
+        raise ValueError(f"Required tensor not found: {name}")
+
+    vocab_size, d_model = shape_of("backbone.embeddings.weight")
+    if shape_of("lm_head.weight") != (vocab_size, d_model):
+        raise ValueError("LM head shape mismatch with embeddings")
+    block_ids = {int(k.split(".")[2]) for k in weight_map if k.startswith("backbone.blocks.") and k.split(".")[2].isdigit()}
+    if not block_ids:
+        raise ValueError("No blocks found in checkpoint")
+    b0 = "backbone.blocks.0"
+    qk_dim = shape_of(f"{b0}.mlstm_layer.q.weight")[0]
+    shape_of(f"{b0}.mlstm_layer.v.weight")
+    ig_b = shape_of(f"{b0}.mlstm_layer.igate_preact.bias")
+    fg_b = shape_of(f"{b0}.mlstm_layer.fgate_preact.bias")
+    up, down = shape_of(f"{b0}.ffn.proj_up.weight"), shape_of(f"{b0}.ffn.proj_down.weight")
+    if down[1] != up[0] or down[0] != d_model:
+        raise ValueError("FFN shape inconsistency")
+    if shape_of(f"{b0}.mlstm_layer.out_proj.weight") != (d_model, d_model):
+        raise ValueError("Output projection shape mismatch")
+    return {"embedding_dim": d_model, "vocab_size": vocab_size, "num_blocks": max(block_ids) + 1,
+            "qk_dim_factor": float(qk_dim / d_model), "v_dim_factor": 1.0, "ffn_proj_factor": float(up[0] / d_model),
+            "num_heads": int(ig_b[0]) if ig_b and ig_b[0] > 0 else 8, "gate_soft_cap": 15.0, "norm_eps": 1e-6,
+            "use_bias": ig_b is not None and fg_b is not None, "output_logit_soft_cap": 30.0, "chunk_size": 64}
+
+
 XLSTM_7B_CONFIG = {
     "embedding_dim": 4096, "num_heads": 8, "num_blocks": 32, "vocab_size": 50304, "qk_dim_factor": 0.5,
     "v_dim_factor": 1.0, "ffn_proj_factor": 2.667, "ffn_round_up_to_multiple_of": 64,
@@ -96,4 +148,5 @@ def write_model_dir(path, config: Dict[str, Any], block_types=None) -> Path:
     return path
 
 
-__all__ = ["resolve_dtype", "load_config", "load_safetensor_shards", "write_model_dir", "XLSTM_7B_CONFIG"]
+__all__ = ["resolve_dtype", "load_config", "load_safetensor_shards", "infer_config_from_safetensors", "write_model_dir",
+           "XLSTM_7B_CONFIG"]
