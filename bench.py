@@ -515,6 +515,21 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
         dist.barrier()
         gat_ms = _time_cuda(torch, lambda: fused.run(q, k, v, i, f, None, out_proj=None, workspace=ws), reps)
     tok_ms, tok_check = None, None
+    if fused is not None and Sp % (128 * world) == 0:
+        # token-sharded variant: a tile of h goes only to the rank owning its tokens; 1/world of the out-projection each
+        from xlstm_cuda.parallel import FusedHeadScatter
+        scat = FusedHeadScatter(Bp, Sp, nh_local * world, DV, bf, device)
+        scat.run(q, k, v, i, f, None, out_proj=w_out.t(), workspace=ws)
+        tok = Sp // world
+        same = torch.tensor([1 if torch.equal(scat.buf, fused.buf[:, rank * tok:(rank + 1) * tok]) else 0], device=device)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        tok_check = "bit-exact" if int(same.item()) == 1 else "MISMATCH"
+        dist.barrier()
+        tok_ms = _time_cuda(torch, lambda: scat.run(q, k, v, i, f, None, out_proj=w_out.t(), workspace=ws), reps)
+        t_tok = torch.tensor([tok_ms], device=device)
+        dist.all_reduce(t_tok, op=dist.ReduceOp.MAX)
+        tok_ms = float(t_tok.item())
+        del scat
     t_cell = torch.tensor([e[0].elapsed_time(e[1]) / reps, e[2].elapsed_time(e[3]) / reps, nccl_ms, gat_ms], device=device)
     if world > 1:
         dist.all_reduce(t_cell, op=dist.ReduceOp.MAX)
@@ -741,7 +756,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--prefill-seq", type=int, default=32768)
-    ap.add_argument("--prefill-reps", type=int, default=3)
+    ap.add_argument("--prefill-reps", type=int, default=10)
     ap.add_argument("--no-extras", action="store_true", help="skip the soft-cap, sLSTM and full-model sub-benchmarks")
     ap.add_argument("--no-model", action="store_true", help="skip the 7B-shaped full-model run")
     ap.add_argument("--glue-only", action="store_true",

@@ -141,6 +141,25 @@ int xlstm_mlstm_chunkwise_fwd_gather(const void *q, const void *k, const void *v
                                      void *const *h_peers, int n_peers, void *stream);
 
 /*
+ * The token-sharded counterpart of xlstm_mlstm_chunkwise_fwd_gather.  With the gather every rank ends up with
+ * ALL tokens of all heads and repeats the whole out-projection; here a tile of h goes ONLY to the rank that
+ * owns its tokens: `h_ranks[r]` (r = 0 .. world-1, this rank's own buffer at its own index; a HOST array of
+ * device pointers) is the slot of THIS rank's heads inside rank r's [B, tokens_per_rank, NH_total, dv] buffer,
+ * tokens [r * tokens_per_rank, (r+1) * tokens_per_rank) of the sequence.  After one cross-rank barrier every
+ * rank holds all heads for S / world tokens and runs 1 / world of the out-projection; each rank sends
+ * (world-1) / world of its h over NVLink instead of world-1 copies of it.  The element strides of h in
+ * `strides` describe those buffers; tokens_per_rank is a multiple of 128 and world * tokens_per_rank == S.
+ * No local copy of h is written.  TMA tile stores, no multicast, no load from peer memory.
+ * Same role in the reference as xlstm_mlstm_chunkwise_fwd_gather (none: single-device).
+ */
+int xlstm_mlstm_chunkwise_fwd_scatter(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                      const float *C0, const float *n0, const float *m0,
+                                      float *C1, float *n1, float *m1,
+                                      int B, int NH, int S, int dqk, int dv, int L, float eps, int dtype,
+                                      const int64_t *strides, void *workspace, size_t workspace_bytes,
+                                      void *const *h_ranks, int world, int tokens_per_rank, void *stream);
+
+/*
  * xlstm_mlstm_chunkwise_fwd for callers that cannot supply scratch memory (no counterpart in
  * the reference: its launchers allocate their outputs through the framework).  Same arguments
  * and results as xlstm_mlstm_chunkwise_fwd without `workspace`; the scratch is an 8 MiB block

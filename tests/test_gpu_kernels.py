@@ -486,3 +486,22 @@ def test_bounded_wait_gives_up_and_status_queries_report_ok(ops):
     ops.mlstm_chunkwise(q, k, v, i, f, workspace=ws)
     ops.chunkwise_status(ws)            # raises on XLSTM_ERR_TIMEOUT
     ops.slstm_recurrent_status()
+
+
+def test_chunkwise_scatter_entry_point_single_rank(ops):
+    """The token-sharded store mode with one rank: h lands in the [B, S, NH, dv] buffer exactly as the regular
+    entry point writes it into a strided view of the same layout (the multi-rank routing is covered by the
+    two-GPU test)."""
+    from xlstm_cuda.parallel import FusedHeadScatter
+    rng = np.random.default_rng(31)
+    B, NH, S, dqk, dv = 2, 2, 512, 128, 256
+    q, k = (dev(rng.standard_normal((B, NH, S, dqk)).astype(np.float32), torch.bfloat16) for _ in range(2))
+    v = dev(rng.standard_normal((B, NH, S, dv)).astype(np.float32), torch.bfloat16)
+    i, f = (dev(a, torch.bfloat16) for a in gates(rng, (B, NH, S)))
+    w = dev((rng.standard_normal((NH * dv, 48)) * 0.05).astype(np.float32), torch.bfloat16)
+    h, st = ops.mlstm_chunkwise(q, k, v, i, f)
+    sc = FusedHeadScatter(B, S, NH, dv, torch.bfloat16, "cuda")
+    y, st2 = sc.run(q, k, v, i, f, None, out_proj=w)
+    assert torch.equal(sc.buf, h.permute(0, 2, 1, 3).contiguous())
+    assert all(torch.equal(a, b) for a, b in zip(st, st2))
+    assert torch.equal(y, h.permute(0, 2, 1, 3).reshape(B, S, NH * dv) @ w)

@@ -2,7 +2,8 @@
 
 Runs as two child processes (one per GPU, NCCL over 127.0.0.1); skipped on a single-GPU box.
 The gathered h must equal, bit for bit, what each rank computes for its own heads, and the fused path
-must equal the NCCL all-gather path.
+must equal the NCCL all-gather path.  The same ranks then run a whole model with head-sharded mLSTM layers
+against the unsharded model.
 """
 import os
 import sys
@@ -44,6 +45,40 @@ def _worker(rank, world, port, tmp):
         ok = ok and torch.equal(h_all, ref)
         y_ref, _ = parallel.head_sharded_prefill(lambda *a: ops.mlstm_chunkwise(*a), q, k, v, i, f, None, out_proj=w)
         ok = ok and torch.allclose(y.float(), y_ref.float(), rtol=1e-2, atol=1e-2)
+    # token-sharded variant: every rank receives all heads of ITS token range only and projects those
+    scatter = parallel.FusedHeadScatter(B, S, NH, dv, bf, dev)
+    for _ in range(2):
+        y_tok, _ = scatter.run(sl(q), sl(k), sl(v), sl(i), sl(f), None, out_proj=w)
+        tok = S // world
+        ok = ok and torch.equal(scatter.buf, ref[:, rank * tok:(rank + 1) * tok])
+        ok = ok and torch.equal(y_tok, ref[:, rank * tok:(rank + 1) * tok].reshape(B, tok, NH * dv) @ w)
+    # model level: every mLSTM layer head-sharded over the two ranks (sliced checkpoint load, local norm x gate,
+    # all-gather of the gated heads, replicated out-projection) against the unsharded model on the same GPU
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    from make_golden_model import TINY
+    from param_init import fill_parameters
+    from xlstm_cuda.models import WiredxLSTM
+    from xlstm_cuda.utils import write_model_dir
+    d = write_model_dir(Path(tmp) / f"tiny{rank}", dict(TINY))
+    full = WiredxLSTM.from_pretrained(d, load_weights=False, device=dev)
+    fill_parameters(dict(full.named_parameters()), seed=21)
+    ckpt = {"backbone.embeddings.weight": full.embedding.weight, "backbone.out_norm.weight": full.out_norm.weight,
+            "lm_head.weight": full.lm_head.weight}
+    for blk in full.blocks:
+        params = dict(blk.named_parameters())
+        ckpt.update({key: params[path] for path, key in blk.get_weight_keys().items()})
+    sharded = WiredxLSTM.from_pretrained(d, load_weights=False, device=dev, head_shard=(rank, world))
+    sharded._load_weights_from_dict({k_: v_.detach() for k_, v_ in ckpt.items()})
+    ids = torch.randint(0, TINY["vocab_size"], (2, 70), generator=torch.Generator().manual_seed(5))
+    with torch.inference_mode():
+        want, st_full = full(ids, None, return_last_states=True)
+        got, st_loc = sharded(ids, None, return_last_states=True)
+        nxt, _ = sharded(ids[:, :1], st_loc, return_last_states=True)      # a decode step carrying the sharded state
+        nxt_ref, _ = full(ids[:, :1], st_full, return_last_states=True)
+    rel = lambda a, b: float((a.float() - b.float()).abs().max() / b.float().abs().max())
+    lo, hi = parallel.head_range(TINY["num_heads"], world, rank)
+    ok = ok and rel(got, want) < 1e-4 and rel(nxt, nxt_ref) < 1e-4
+    ok = ok and all(rel(a[0], b[0][:, lo:hi]) < 1e-4 for a, b in zip(st_loc, st_full))
     torch.cuda.synchronize()
     Path(tmp, f"ok{rank}").write_text("1" if ok else "0")
     dist.destroy_process_group()

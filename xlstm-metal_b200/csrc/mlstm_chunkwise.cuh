@@ -15,8 +15,11 @@ struct ChunkwiseParams {
     // element strides (batch, head, token); innermost dimension contiguous
     int64_t sq[3], sk[3], sv[3], sh[3], sg[3];
     // optional extra destinations of h (same strides and offsets as `h`): buffers of peer GPUs
-    void *h_peer[7];
+    void *h_peer[8];
     int n_peer;
+    // > 0: token-sharded destinations instead of replicas - h_peer[r] (r = 0 .. n_peer-1, this rank included, `h` unused)
+    // is rank r's [B, tok_per_rank, NH_total, dv] buffer and a tile of tokens goes ONLY to the rank that owns them
+    int tok_per_rank;
 };
 
 // exact-fp32 CUDA-core path: any dqk <= 512, dv, S, L <= 64

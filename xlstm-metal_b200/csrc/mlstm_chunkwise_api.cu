@@ -52,8 +52,8 @@ static int chunkwise_dispatch(const void *q, const void *k, const void *v, const
                               float *n1, float *m1, int B, int NH, int S, int dqk, int dv, int L,
                               float eps, int dtype, const int64_t *strides, void *workspace,
                               size_t workspace_bytes, void *stream, void *const *h_peers, int n_peers,
-                              float gate_cap = 0.0f) {
-    if (!q || !k || !v || !ig || !fg || !h || !C1 || !n1 || !m1) return XLSTM_ERR_INVALID;
+                              float gate_cap = 0.0f, int tok_per_rank = 0) {
+    if (!q || !k || !v || !ig || !fg || (!h && tok_per_rank <= 0) || !C1 || !n1 || !m1) return XLSTM_ERR_INVALID;
     if (B <= 0 || NH <= 0 || S <= 0 || dqk <= 0 || dv <= 0 || L <= 0) return XLSTM_ERR_INVALID;
     if (C0 && (!n0 || !m0)) return XLSTM_ERR_INVALID;
     if (C0 && (C1 == C0 || n1 == n0 || m1 == m0)) return XLSTM_ERR_INVALID;
@@ -77,8 +77,10 @@ static int chunkwise_dispatch(const void *q, const void *k, const void *v, const
         dense_strides(p);
     }
 
-    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !h_peers)) return XLSTM_ERR_INVALID;
+    if (n_peers < 0 || n_peers > (tok_per_rank > 0 ? 8 : 7) || (n_peers > 0 && !h_peers)) return XLSTM_ERR_INVALID;
+    if (tok_per_rank > 0 && n_peers < 1) return XLSTM_ERR_INVALID;
     p.n_peer = n_peers;
+    p.tok_per_rank = tok_per_rank > 0 ? tok_per_rank : 0;
     for (int i = 0; i < n_peers; ++i) {
         if (!h_peers[i] || (reinterpret_cast<uintptr_t>(h_peers[i]) & 15u)) return XLSTM_ERR_INVALID;
         p.h_peer[i] = h_peers[i];
@@ -115,6 +117,17 @@ extern "C" int xlstm_mlstm_chunkwise_fwd_gather(const void *q, const void *k, co
                                                 int n_peers, void *stream) {
     return chunkwise_dispatch(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, S, dqk, dv, L, eps, dtype, strides,
                               workspace, workspace_bytes, stream, h_peers, n_peers);
+}
+
+extern "C" int xlstm_mlstm_chunkwise_fwd_scatter(const void *q, const void *k, const void *v, const void *ig,
+                                                 const void *fg, const float *C0, const float *n0, const float *m0,
+                                                 float *C1, float *n1, float *m1, int B, int NH, int S, int dqk, int dv,
+                                                 int L, float eps, int dtype, const int64_t *strides, void *workspace,
+                                                 size_t workspace_bytes, void *const *h_ranks, int world,
+                                                 int tokens_per_rank, void *stream) {
+    if (tokens_per_rank <= 0) return XLSTM_ERR_INVALID;
+    return chunkwise_dispatch(q, k, v, ig, fg, C0, n0, m0, nullptr, C1, n1, m1, B, NH, S, dqk, dv, L, eps, dtype, strides,
+                              workspace, workspace_bytes, stream, h_ranks, world, 0.0f, tokens_per_rank);
 }
 
 extern "C" int xlstm_mlstm_chunkwise_fwd_gatecap(const void *q, const void *k, const void *v, const void *ig,

@@ -441,9 +441,16 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_kernel(const __
         if (lane == 0) {
             for (int k = 0; k < NCH; ++k) {
                 if (!mbar_wait(&bars[B_HSTAGED], k & 1, abort_flag)) break;
-                for (int d = 0; d < p.n_h; ++d)
+                const int tk = (tile0 + k) * LT;
+                if (p.tok_per_rank > 0 && p.n_h > 0) {   // token-sharded: only the rank that owns these tokens gets the tile
+                    const int d = tk / p.tok_per_rank;
                     for (int bx = 0; bx < 2; ++bx)
-                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, (tile0 + k) * LT, hd, b);
+                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, tk - d * p.tok_per_rank, hd, b);
+                } else {
+                    for (int d = 0; d < p.n_h; ++d)
+                        for (int bx = 0; bx < 2; ++bx)
+                            tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, tk, hd, b);
+                }
                 tma_store_commit();
                 tma_store_wait_read();            // staging tile consumed: V may be reloaded
                 mbar_arrive(&bars[B_VFREE]);
@@ -671,7 +678,7 @@ bool mlstm_chunkwise_tc_shape_ok(const ChunkwiseParams &p, int dtype) {
     for (int d = 0; d < 3; ++d)
         if (p.sq[d] % 8 || p.sk[d] % 8 || p.sv[d] % 8 || p.sh[d] % 8) return false;  // 16-byte TMA / store alignment
     if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
-         reinterpret_cast<uintptr_t>(p.h)) & 15u)
+         reinterpret_cast<uintptr_t>(p.h)) & 15u)   // (h is NULL in the token-sharded mode)
         return false;
     if (p.dv / DVS > 65535) return false;
     return true;
@@ -780,6 +787,7 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
     float *segB_m = reinterpret_cast<float *>(ws + w.seg_m[1]);
     const bool tail = s_full < p.S;
     if (tail && p.n_peer) return XLSTM_ERR_UNSUPPORTED;   // the exact tail path writes the local h only
+    if (p.tok_per_rank > 0 && (p.tok_per_rank % LT || (long long)p.tok_per_rank * p.n_peer != s_full)) return XLSTM_ERR_INVALID;
     if (cudaMemsetAsync(status, 0, sizeof(int), st) != cudaSuccess) return XLSTM_ERR_CUDA;
 
     const __nv_bfloat16 *ig = static_cast<const __nv_bfloat16 *>(p.ig), *fg = static_cast<const __nv_bfloat16 *>(p.fg);
@@ -793,9 +801,14 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
         !make_tmap_bf16_4d(&tp.tk, p.k, p.dqk, s_full, p.NH, p.B, p.sk[2], p.sk[1], p.sk[0], LT) ||
         !make_tmap_bf16_4d(&tp.tv, p.v, p.dv, s_full, p.NH, p.B, p.sv[2], p.sv[1], p.sv[0], LT))
         return XLSTM_ERR_UNSUPPORTED;
-    for (int i = 0; i < 1 + p.n_peer; ++i)
-        if (!make_tmap_bf16_4d(&tp.th[i], i == 0 ? p.h : p.h_peer[i - 1], p.dv, s_full, p.NH, p.B, p.sh[2], p.sh[1], p.sh[0], LT))
+    const int n_dest = p.tok_per_rank > 0 ? p.n_peer : 1 + p.n_peer;
+    for (int i = 0; i < n_dest; ++i) {
+        void *dst = p.tok_per_rank > 0 ? p.h_peer[i] : (i == 0 ? p.h : p.h_peer[i - 1]);
+        if (!make_tmap_bf16_4d(&tp.th[i], dst, p.dv, p.tok_per_rank > 0 ? p.tok_per_rank : s_full, p.NH, p.B, p.sh[2], p.sh[1],
+                               p.sh[0], LT))
             return XLSTM_ERR_UNSUPPORTED;
+    }
+    tp.tok_per_rank = p.tok_per_rank;
     tp.gates = gates;
     tp.NH = p.NH; tp.dv = p.dv; tp.NCH = nch; tp.eps = p.eps; tp.log2_qscale = log2f(p.qscale); tp.status = status;
     tp.path = path; tp.h = p.h; tp.P = P; tp.seg_tiles = seg_tiles;
@@ -829,13 +842,12 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
 
     float *n_final = tail ? tail_n : p.n1, *m_final = tail ? tail_m : p.m1;
     if (P == 1) {
-        tp.C0 = p.C0; tp.n0 = p.n0; tp.C1 = p.C1; tp.n1 = n_final; tp.n_h = 1 + p.n_peer;
+        tp.C0 = p.C0; tp.n0 = p.n0; tp.C1 = p.C1; tp.n1 = n_final; tp.n_h = n_dest;
         const int rc = forward(p.C0 ? p.m0 : nullptr, 0, m_final);
         if (rc != XLSTM_OK) return rc;
     } else {
-        // pass 1: every segment from an empty state -> its local end state (h is written too and overwritten by pass 2;
-        // nothing goes to the peers yet)
-        tp.C0 = nullptr; tp.n0 = nullptr; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = 1;
+        // pass 1: every segment from an empty state -> its local end state (its h is wrong and is not stored anywhere)
+        tp.C0 = nullptr; tp.n0 = nullptr; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = 0;
         int rc = forward(nullptr, 1, segA_m);
         if (rc != XLSTM_OK) return rc;
         // the true state at the start of every segment, and the final state
@@ -845,7 +857,7 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
             m_final, nch, P, seg_tiles, p.dqk, p.dv);
         if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
         // pass 2: every segment from its true start state
-        tp.C0 = segB_C; tp.n0 = segB_n; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = 1 + p.n_peer;
+        tp.C0 = segB_C; tp.n0 = segB_n; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = n_dest;
         rc = forward(segB_m, 0, segA_m);
         if (rc != XLSTM_OK) return rc;
     }

@@ -23,7 +23,8 @@ struct TcParams {
     const float *gates;            // [B*NH][NCH][GW]
     const float *C0, *n0;
     CUtensorMap th[8];             // h of this GPU, then the same head slot of up to 7 peer GPUs' buffers
-    int n_h;                       // number of destinations (1 + peers)
+    int n_h;                       // number of destinations (1 + peers); 0: h is not stored at all
+    int tok_per_rank;              // > 0: th[r] is rank r's token-sharded buffer; a tile goes to the owner of its tokens only
     float *C1, *n1;
     int NH, dv, NCH;
     float eps, log2_qscale;

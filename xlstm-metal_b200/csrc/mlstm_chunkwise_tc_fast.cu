@@ -289,9 +289,16 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
         if (lane == 0) {
             for (int k = 0; k < NCH; ++k) {
                 if (!mbar_wait(&bars[F_HSTAGED], k & 1, abort_flag)) break;
-                for (int d = 0; d < p.n_h; ++d)
+                const int tk = (tile0 + k) * LT;
+                if (p.tok_per_rank > 0 && p.n_h > 0) {   // token-sharded: only the rank that owns these tokens gets the tile
+                    const int d = tk / p.tok_per_rank;
                     for (int bx = 0; bx < 2; ++bx)
-                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, (tile0 + k) * LT, hd, b);
+                        tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, tk - d * p.tok_per_rank, hd, b);
+                } else {
+                    for (int d = 0; d < p.n_h; ++d)
+                        for (int bx = 0; bx < 2; ++bx)
+                            tma_store_4d(&p.th[d], smem + SM::V + bx * SM::BOX, col0 + bx * 64, tk, hd, b);
+                }
                 tma_store_commit();
                 tma_store_wait_read();            // staging tile consumed: V may be reloaded
                 mbar_arrive(&bars[F_VFREE]);

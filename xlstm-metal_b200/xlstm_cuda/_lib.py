@@ -23,6 +23,9 @@ _SIGNATURES = {
     "xlstm_mlstm_chunkwise_fwd_gather": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6
                                          + [c_float, c_int, ctypes.POINTER(c_int64), c_void_p, c_size_t,
                                             ctypes.POINTER(c_void_p), c_int, c_void_p]),
+    "xlstm_mlstm_chunkwise_fwd_scatter": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 3 + [c_int] * 6
+                                          + [c_float, c_int, ctypes.POINTER(c_int64), c_void_p, c_size_t,
+                                             ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
     "xlstm_mlstm_chunkwise_workspace_bytes": (c_size_t, [c_int] * 7),
     "xlstm_mlstm_chunkwise_set_general_only": (c_int, [c_int]),
     "xlstm_mlstm_chunkwise_set_segments": (c_int, [c_int]),

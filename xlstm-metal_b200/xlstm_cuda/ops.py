@@ -182,6 +182,42 @@ def mlstm_chunkwise(q, k, v, i, f, state=None, chunk_size: int = 64, eps: float 
     return h, (C1, n1, m1)
 
 
+def mlstm_chunkwise_scatter(q, k, v, i, f, state, h_rank_ptrs, tokens_per_rank: int, h_strides, chunk_size: int = 64,
+                            eps: float = 1e-6, workspace: Optional[torch.Tensor] = None):
+    """Chunkwise forward whose h tiles go to the rank that owns their tokens (``h_rank_ptrs[r]`` = this rank's
+    head slot in rank r's ``[B, tokens_per_rank, NH_total, dv]`` buffer, ``h_strides`` = its (batch, head, token)
+    element strides).  Returns the final state only; h lives in the ranks' buffers."""
+    _need_cuda(q, k, v, i, f)
+    B, NH, S, dqk = q.shape
+    dv = v.shape[-1]
+    fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
+    q, k, v = fix(q), fix(k.to(q.dtype)), fix(v.to(q.dtype))
+    i, f = i.to(q.dtype), f.to(q.dtype)
+    if i.stride() != f.stride():
+        i, f = i.contiguous(), f.contiguous()
+    if state is not None:
+        C0, n0, m0 = (_state32(s) for s in state)
+        m0 = m0.reshape(B, NH)
+    else:
+        C0 = n0 = m0 = None
+    dev = q.device
+    C1 = torch.empty(B, NH, dqk, dv, dtype=torch.float32, device=dev)
+    n1 = torch.empty(B, NH, dqk, dtype=torch.float32, device=dev)
+    m1 = torch.empty(B, NH, dtype=torch.float32, device=dev)
+    strides = _strides3(q) + _strides3(k) + _strides3(v) + list(h_strides) + [i.stride(0), i.stride(1), i.stride(2)]
+    sarr = (ctypes.c_int64 * 15)(*strides)
+    need = chunkwise_workspace_bytes(B, NH, S, dqk, dv, chunk_size, q.dtype)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    ranks = (ctypes.c_void_p * len(h_rank_ptrs))(*[int(x) for x in h_rank_ptrs])
+    _lib.check(_lib.load().xlstm_mlstm_chunkwise_fwd_scatter(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
+        C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, S, dqk, dv, int(chunk_size), float(eps), _dtype_code(q), sarr,
+        _ptr(workspace), workspace.numel() * workspace.element_size(), ranks, len(h_rank_ptrs), int(tokens_per_rank),
+        _stream()), "xlstm_mlstm_chunkwise_fwd_scatter")
+    return C1, n1, m1
+
+
 def slstm_scan(z, i, f, o, state=None, eps: float = 1e-6):
     """Packaged sLSTM cell over S steps.  z: [B,S,NH,H]; i,f,o: [B,S,NH]; state (c,n,m) or None."""
     _need_cuda(z, i, f, o)

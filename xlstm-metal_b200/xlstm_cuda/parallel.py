@@ -129,3 +129,52 @@ class FusedHeadGather:
 
 
 __all__ = ["head_range", "batch_range", "shard_heads", "all_gather_heads", "head_sharded_prefill", "FusedHeadGather"]
+
+
+class FusedHeadScatter:
+    """Head-sharded chunkwise prefill with a TOKEN-sharded result: every rank ends up with all heads of
+    ``S / world`` tokens and runs ``1 / world`` of the out-projection.
+
+    Every rank owns a ``[B, S/world, NH, dv]`` buffer in symmetric memory.  The chunkwise kernel of rank r sends each
+    h tile of its heads, by a TMA tile store, only to the rank that owns the tile's tokens (its own buffer for its
+    own token range): ``(world-1)/world`` of h crosses NVLink once, where the all-gather layout of
+    ``FusedHeadGather`` sends ``world-1`` copies and then repeats the full out-projection on every rank.  The
+    output ``[B, S/world, D]`` is the token slice of this rank, which is what the per-token residual, norm and
+    FFN that follow need.
+    """
+
+    def __init__(self, B: int, S: int, NH: int, dv: int, dtype: torch.dtype, device, group=None):
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
+        self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+        if S % (128 * self.world):
+            raise ValueError("S must be a multiple of 128 * world for the token-sharded layout")
+        self.B, self.S, self.NH, self.dv, self.tok = B, S, NH, dv, S // self.world
+        self.lo, self.hi = head_range(NH, self.world, self.rank)
+        self.handle = None
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buf = symm_mem.empty(B, self.tok, NH, dv, dtype=dtype, device=device)
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+            ptrs = [int(x) for x in self.handle.buffer_ptrs]
+        else:
+            self.buf = torch.empty(B, self.tok, NH, dv, dtype=dtype, device=device)
+            ptrs = [self.buf.data_ptr()]
+        slot = self.lo * dv * self.buf.element_size()   # this rank's first head inside any rank's buffer
+        self.rank_ptrs = [ptr + slot for ptr in ptrs]
+        self.h_strides = [self.tok * NH * dv, dv, NH * dv]   # (batch, head, token) element strides of the buffers
+
+    def barrier(self) -> None:
+        if self.handle is not None:
+            self.handle.barrier()
+
+    def run(self, q, k, v, i, f, state=None, out_proj: Optional[torch.Tensor] = None, workspace=None):
+        """q, k, v, i, f hold THIS rank's heads.  Returns ``(y or h, state)`` for this rank's tokens
+        ``[rank*S/world, (rank+1)*S/world)``: ``[B, S/world, D]`` or ``[B, S/world, NH*dv]``."""
+        from . import ops
+        self.barrier()   # peers are done reading the previous contents of their buffers
+        st = ops.mlstm_chunkwise_scatter(q, k, v, i, f, state, self.rank_ptrs, self.tok, self.h_strides, workspace=workspace)
+        self.barrier()   # every rank's kernel has finished: all head slots of this rank's tokens are written
+        h_tok = self.buf.view(self.B, self.tok, self.NH * self.dv)
+        return (h_tok if out_proj is None else h_tok @ out_proj), st
+
