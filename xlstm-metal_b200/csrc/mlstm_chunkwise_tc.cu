@@ -702,14 +702,17 @@ constexpr int SM_COUNT = 148;          // B200
 constexpr int MIN_SEG_TILES = 16;      // a shorter segment is dominated by its prologue (state in) and epilogue (state out)
 
 // Number of segments every sequence is cut into: while the grid of persistent CTAs (one per head and 128 dv
-// columns) fills less than a third of the SMs, cutting the sequence buys parallelism at the price of a second
-// pass (two passes over 1/P of the sequence: a gain from P = 3).
+// columns) fills at most half of the SMs, cutting the sequence buys parallelism at the price of the state-only
+// first pass (about a quarter of a full pass) and of the states going through HBM once.
 int plan_segments(int BH, int dv, int nch) {
     const int ctas = BH * (dv / DVS);
     int P = SM_COUNT / ctas;
     if (P > nch / MIN_SEG_TILES) P = nch / MIN_SEG_TILES;
     if (P > 64) P = 64;
-    return P < 3 ? 1 : P;
+    if (P < 2) return 1;
+    for (int d = P; 4 * d >= 3 * P; --d)      // segments of equal length, if a count close to P divides the tiles
+        if (nch % d == 0) return d;
+    return P;
 }
 
 WsLayout ws_layout(int B, int NH, int S, int dqk, int dv, int P) {
@@ -818,13 +821,13 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
     // one forward over all (head, segment) pairs: chain + per-token scalars of the gate pre-pass, then the two
     // tensor-core kernels.  Two launches over the same grid: every CTA looks at its path flag (written by the
     // pre-pass) and returns at once if it belongs to the other kernel, so the choice needs no host round trip.
-    auto forward = [&](const float *m0v, int m0_auto, float *m_out) -> int {
+    auto forward = [&](const float *m0v, int m0_auto, float *m_out, bool state_only) -> int {
         mlstm_gate_chain_kernel<<<BH * P, 32, 0, st>>>(m0v, chain, m_out, path, nch, P, seg_tiles, g_general_only.load(),
                                                        m0_auto);
         mlstm_gate_write_kernel<__nv_bfloat16><<<tg, GP_THREADS, 0, st>>>(ig, fg, p.sg[0], p.sg[1], p.sg[2], chain, path, gates,
                                                                           p.NH, nch, P, seg_tiles, p.qscale, p.gate_cap);
         if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
-        const int rc = mlstm_chunkwise_tc_fast_launch(tp, grid, p.dqk, st);
+        const int rc = state_only ? mlstm_chunkwise_tc_scan_launch(tp, grid, p.dqk, st) : mlstm_chunkwise_tc_fast_launch(tp, grid, p.dqk, st);
         if (rc != XLSTM_OK) return rc;
         if (p.dqk == 256) {
             auto kern = mlstm_chunkwise_tc_kernel<256>;
@@ -843,12 +846,13 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
     float *n_final = tail ? tail_n : p.n1, *m_final = tail ? tail_m : p.m1;
     if (P == 1) {
         tp.C0 = p.C0; tp.n0 = p.n0; tp.C1 = p.C1; tp.n1 = n_final; tp.n_h = n_dest;
-        const int rc = forward(p.C0 ? p.m0 : nullptr, 0, m_final);
+        const int rc = forward(p.C0 ? p.m0 : nullptr, 0, m_final, false);
         if (rc != XLSTM_OK) return rc;
     } else {
-        // pass 1: every segment from an empty state -> its local end state (its h is wrong and is not stored anywhere)
+        // pass 1: every segment from an empty state -> its local end state: the state-only scan kernel (segments whose
+        // gates need the general kernel run that one in full, with nothing stored)
         tp.C0 = nullptr; tp.n0 = nullptr; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = 0;
-        int rc = forward(nullptr, 1, segA_m);
+        int rc = forward(nullptr, 1, segA_m, true);
         if (rc != XLSTM_OK) return rc;
         // the true state at the start of every segment, and the final state
         const int slabs = (int)((CE + p.dqk + 64 * COMB_THREADS - 1) / (64 * COMB_THREADS));
@@ -858,7 +862,7 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
         if (cudaGetLastError() != cudaSuccess) return XLSTM_ERR_CUDA;
         // pass 2: every segment from its true start state
         tp.C0 = segB_C; tp.n0 = segB_n; tp.C1 = segA_C; tp.n1 = segA_n; tp.n_h = n_dest;
-        rc = forward(segB_m, 0, segA_m);
+        rc = forward(segB_m, 0, segA_m, false);
         if (rc != XLSTM_OK) return rc;
     }
     if (!tail) return XLSTM_OK;

@@ -189,5 +189,7 @@ __device__ __forceinline__ void c_init_half(unsigned char *smem, uint32_t t_half
 
 // the kernel for gates of bounded in-tile spread (mlstm_chunkwise_tc_fast.cu); CTAs of other heads return at once
 int mlstm_chunkwise_tc_fast_launch(const tcw::TcParams &tp, dim3 grid, int dqk, cudaStream_t st);
+// state-only scan of every segment from an empty state (mlstm_chunkwise_tc_scan.cu): C1, n1 only, no h
+int mlstm_chunkwise_tc_scan_launch(const tcw::TcParams &tp, dim3 grid, int dqk, cudaStream_t st);
 
 }  // namespace xl
