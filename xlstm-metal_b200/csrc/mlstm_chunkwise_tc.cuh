@@ -100,9 +100,13 @@ __device__ __forceinline__ void qn_pass(const unsigned char *smem, const float *
         for (int i = 0; i < 4; ++i) part[rr][i] = 0.f;
 #pragma unroll
         for (int q = 0; q < NBOX; ++q) {
-            const float *np = s_n + q * 64 + ((c ^ rho) << 3);
-            const float4 na = *reinterpret_cast<const float4 *>(np);
-            const float4 nb = *reinterpret_cast<const float4 *>(np + 4);
+            // the lane's 8 values of n: two 16-byte loads, issued in an order that puts the 8 lanes of a
+            // quarter-warp on 8 different 16-byte bank groups (lanes with logical chunk >= 4 take the upper half first)
+            const int cx = c ^ rho, sw = (cx >> 2) & 1;
+            const float *np = s_n + q * 64 + (cx << 3);
+            const float4 x0 = *reinterpret_cast<const float4 *>(np + 4 * sw);
+            const float4 x1 = *reinterpret_cast<const float4 *>(np + 4 * (1 - sw));
+            const float4 na = sw ? x1 : x0, nb = sw ? x0 : x1;
             const unsigned char *base = smem + SM::Q + q * SM::BOX + row0 * 128 + (c << 4);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
