@@ -297,8 +297,12 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_simt_kernel(Chunkw
 
 }  // namespace
 
-int mlstm_chunkwise_simt(const ChunkwiseParams &p, int dtype, cudaStream_t st) {
-    if (p.L < 1 || p.L > LT) return XLSTM_ERR_UNSUPPORTED;
+int mlstm_chunkwise_simt(const ChunkwiseParams &p_in, int dtype, cudaStream_t st) {
+    if (p_in.L < 1) return XLSTM_ERR_UNSUPPORTED;
+    // The chunkwise form is a re-association of the recurrence: any internal tile gives the same result, so a
+    // chunk size beyond the kernel's tile is walked in tiles of LT tokens instead of being refused.
+    ChunkwiseParams p = p_in;
+    if (p.L > LT) p.L = LT;
     if (p.dqk % 4 || p.dv % 4) return XLSTM_ERR_UNSUPPORTED;
     for (int d = 0; d < 3; ++d)
         if (p.sq[d] % 4 || p.sk[d] % 4 || p.sv[d] % 4 || p.sh[d] % 4) return XLSTM_ERR_UNSUPPORTED;

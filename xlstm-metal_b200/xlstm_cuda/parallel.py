@@ -128,9 +128,6 @@ class FusedHeadGather:
         return (h_all if out_proj is None else h_all @ out_proj), st
 
 
-__all__ = ["head_range", "batch_range", "shard_heads", "all_gather_heads", "head_sharded_prefill", "FusedHeadGather"]
-
-
 class FusedHeadScatter:
     """Head-sharded chunkwise prefill with a TOKEN-sharded result: every rank ends up with all heads of
     ``S / world`` tokens and runs ``1 / world`` of the out-projection.
@@ -178,3 +175,6 @@ class FusedHeadScatter:
         h_tok = self.buf.view(self.B, self.tok, self.NH * self.dv)
         return (h_tok if out_proj is None else h_tok @ out_proj), st
 
+
+__all__ = ["head_range", "batch_range", "shard_heads", "all_gather_heads", "all_gather_features", "head_sharded_prefill",
+           "FusedHeadGather", "FusedHeadScatter"]
