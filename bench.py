@@ -255,7 +255,9 @@ def run_ours(args):
     m = [[torch.zeros(B, NH, device=device), torch.empty(B, NH, device=device)] for _ in range(N_LAYERS)]
     h = torch.empty(B, NH, DV, dtype=torch.bfloat16, device=device)
     # pointer tuples for every (input set, layer, side): the timed loop is then one C call per step
-    fn = lib.xlstm_mlstm_step
+    # the ring of layers guarantees that a step's state was written 8 launches earlier, so its first state rows may
+    # be fetched while the preceding launch drains (XLSTM_STEP_STATE_SETTLED)
+    fn = lib.xlstm_mlstm_step_ex
     ptr = {}
     for s_ in range(N_INPUT_SETS):
         for l in range(N_LAYERS):
@@ -266,14 +268,14 @@ def run_ours(args):
                 ptr[(s_, l, a)] = (qd[s_].data_ptr(), kd[s_].data_ptr(), vd[s_].data_ptr(), idv[s_].data_ptr(),
                                    fd[s_].data_ptr(), C[l][a].data_ptr(), n[l][a].data_ptr(), m[l][a].data_ptr(),
                                    h.data_ptr(), C[l][b].data_ptr(), n[l][b].data_ptr(), m[l][b].data_ptr(),
-                                   B, NH, DQK, DV, 1e-6, _lib.BF16)
+                                   B, NH, DQK, DV, 1e-6, 0.0, _lib.STEP_STATE_SETTLED, _lib.BF16)
     side = [0] * N_LAYERS
 
     def step(t, stream):
         l = t % N_LAYERS
         st = fn(*ptr[(t % N_INPUT_SETS, l, side[l])], stream)
         if st:
-            _lib.check(st, "xlstm_mlstm_step")
+            _lib.check(st, "xlstm_mlstm_step_ex")
         side[l] ^= 1
 
     def barrier():
@@ -333,7 +335,7 @@ def run_ours(args):
         l = t % N_LAYERS
         a = side2[l]
         pipe.step(packed[t % N_INPUT_SETS], (C[l][a], n[l][a], m[l][a]), (C[l][a ^ 1], n[l][a ^ 1], m[l][a ^ 1]),
-                  h_host[t % 2])
+                  h_host[t % 2], state_settled=True)
         side2[l] ^= 1
 
     for t in range(W):
@@ -351,7 +353,7 @@ def run_ours(args):
             l = t % N_LAYERS
             a = side2[l]
             steps_e.append((packed[t % N_INPUT_SETS], (C[l][a], n[l][a], m[l][a]),
-                            (C[l][a ^ 1], n[l][a ^ 1], m[l][a ^ 1]), h_host[t % 2]))
+                            (C[l][a ^ 1], n[l][a ^ 1], m[l][a ^ 1]), h_host[t % 2], True))
             side2[l] ^= 1
         egraph = pipe.capture(steps_e)
         egraph.replay()

@@ -240,6 +240,26 @@ int xlstm_mlstm_step_gatecap(const void *q, const void *k, const void *v, const 
                              const float *C0, const float *n0, const float *m0,
                              void *h, float *C1, float *n1, float *m1,
                              int B, int NH, int dqk, int dv, float eps, float gate_cap, int dtype, void *stream);
+/*
+ * The decode step with launch flags.  All single-token kernels of this library (xlstm_mlstm_step*,
+ * xlstm_linear_token, xlstm_mlstm_output_gate) are launched with programmatic stream serialisation: their
+ * CTAs may become resident while the kernel before them in the stream is still draining, and they wait for
+ * that kernel before they touch anything it could have written.  What a kernel may read BEFORE that wait is
+ * what the preceding kernel cannot have written: the weight matrix in xlstm_linear_token, and here, with
+ *   XLSTM_STEP_STATE_SETTLED   the caller promises that C0 was not written by the kernel launched
+ *                              immediately before this call on the stream (true in a layer stack, where a
+ *                              layer's step follows that layer's projection; NOT true when the same state
+ *                              is stepped twice in a row with nothing in between),
+ * the first rows of the state, so that the HBM stream does not stop at the kernel boundary.  Without the flag
+ * (and through xlstm_mlstm_step / xlstm_mlstm_step_gatecap) nothing is read early.  gate_cap <= 0: no cap.
+ * No counterpart in the reference (its recurrent cell is a sequence of torch ops).
+ */
+#define XLSTM_STEP_STATE_SETTLED 1
+int xlstm_mlstm_step_ex(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                        const float *C0, const float *n0, const float *m0,
+                        void *h, float *C1, float *n1, float *m1,
+                        int B, int NH, int dqk, int dv, float eps, float gate_cap, int flags, int dtype,
+                        void *stream);
 int xlstm_mlstm_chunkwise_fwd_gatecap(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                                       const float *C0, const float *n0, const float *m0,
                                       void *h, float *C1, float *n1, float *m1,

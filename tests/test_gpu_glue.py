@@ -55,6 +55,31 @@ def test_rms_norm_shapes(ops, rows, cols, dtype):
     assert relerr(host(y0), xo.rmsnorm(x, None, 1e-6)) <= (FP32_TOL if dtype == torch.float32 else BF16_TOL)
 
 
+@pytest.mark.parametrize("rows,cols", [(3, 4096), (300, 4096), (2000, 4096), (1500, 1024), (1300, 2048), (1200, 96),
+                                       (1187, 4104)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rms_norm_shapes(ops, rows, cols, dtype):
+    """Residual add + RMSNorm: few rows (CTA per row) and many rows (the streamed kernel, >= 1184 rows), widths that
+    fill the warp's vectors exactly and ones that do not.  The sum is rounded to the activation type, stored as
+    the new residual stream, and the norm is taken of the rounded value."""
+    rng = np.random.default_rng(rows * 7 + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32) * 2.0
+    r = rng.standard_normal((rows, cols)).astype(np.float32) * 2.0
+    w = rng.uniform(0.5, 1.5, cols).astype(np.float32)
+    if dtype == torch.bfloat16:
+        x, r, w = bf(x), bf(r), bf(w)
+    s_ref = x + r
+    if dtype == torch.bfloat16:
+        s_ref = bf(s_ref)
+    y_ref = xo.rmsnorm(s_ref, w, 1e-6)
+    s, y = ops.add_rms_norm(dev(x, dtype), dev(r, dtype), dev(w, dtype), 1e-6)
+    np.testing.assert_array_equal(host(s), s_ref)                  # one rounding of an exact fp32 sum
+    assert relerr(host(y), y_ref) <= (FP32_TOL if dtype == torch.float32 else BF16_TOL)
+    s2, y2 = ops.add_rms_norm(dev(x, dtype), dev(r, dtype), None, 1e-6)
+    assert torch.equal(s2, s)
+    assert relerr(host(y2), xo.rmsnorm(s_ref, None, 1e-6)) <= (FP32_TOL if dtype == torch.float32 else BF16_TOL)
+
+
 def test_rms_norm_empty_and_batched(ops):
     assert ops.rms_norm(torch.empty(0, 64, device="cuda"), None).shape == (0, 64)
     x = torch.randn(2, 3, 5, 64, device="cuda")
@@ -83,7 +108,9 @@ def test_output_gate_golden(ops, golden):
     np.testing.assert_allclose(host(y), g["og_y"], rtol=1e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("B,NH,S,dv", [(1, 8, 1, 512), (2, 4, 33, 64), (1, 2, 5, 1024), (3, 8, 130, 512), (2, 3, 7, 48)])
+@pytest.mark.parametrize("B,NH,S,dv", [(1, 8, 1, 512), (2, 4, 33, 64), (1, 2, 5, 1024), (3, 8, 130, 512), (2, 3, 7, 48),
+                                       # more rows than warps in the grid: a warp walks several rows of its head
+                                       (2, 8, 1500, 512), (2, 3, 2500, 48), (3, 5, 1111, 256)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_output_gate_shapes_and_strides(ops, B, NH, S, dv, dtype):
     rng = np.random.default_rng(B * 7 + NH * 11 + S * 13 + dv)
@@ -139,7 +166,9 @@ def test_causal_conv_golden(ops, golden):
 
 
 @pytest.mark.parametrize("B,S,C,K", [(1, 1, 64, 4), (2, 2, 64, 4), (2, 16, 128, 4), (3, 17, 1024, 4), (2, 100, 40, 2),
-                                     (1, 33, 256, 8), (2, 5, 64, 1)])
+                                     (1, 33, 256, 8), (2, 5, 64, 1),
+                                     # long runs per thread: the shared-memory ring is refilled (32 / 64 / 128 tokens)
+                                     (4, 4099, 1040, 4), (16, 4096, 1024, 4), (32, 4100, 1024, 3), (24, 2051, 512, 8)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_causal_conv_shapes_and_state(ops, B, S, C, K, dtype):
     rng = np.random.default_rng(B + 3 * S + 5 * C + 7 * K)

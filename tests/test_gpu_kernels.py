@@ -134,6 +134,64 @@ def test_mlstm_step_config2_256_steps_bf16(ops):
     assert np.abs(host(st[2]) - st_ref[2]).max() < 1e-3
 
 
+def test_mlstm_step_layer_ring_overlapped_launches(ops):
+    """A stack of layers stepped token by token with state_settled=True (each launch may start fetching its
+    state while the launch before it - another layer - drains), eagerly and replayed as a CUDA graph, against
+    the oracle stepping every layer on its own; and the same state stepped twice in a row WITHOUT the promise."""
+    B, NH, dqk, dv, LAYERS, T = 2, 4, 128, 256, 3, 6
+    rng = np.random.default_rng(77)
+    q, k = (rng.standard_normal((LAYERS, B, NH, T, dqk)).astype(np.float32) for _ in range(2))
+    v = rng.standard_normal((LAYERS, B, NH, T, dv)).astype(np.float32)
+    i, f = gates(rng, (LAYERS, B, NH, T))
+    st0 = [(rng.standard_normal((B, NH, dqk, dv)).astype(np.float32) * 0.1,
+            rng.standard_normal((B, NH, dqk)).astype(np.float32) * 0.1, np.zeros((B, NH), np.float32)) for _ in range(LAYERS)]
+    ref = [xo.mlstm_recurrent(q[l], k[l], v[l], i[l], f[l], st0[l]) for l in range(LAYERS)]
+    qd, kd, vd, idv, fd = (dev(a) for a in (q, k, v, i, f))
+
+    def run(states, hs):
+        for t in range(T):
+            for l in range(LAYERS):
+                h, states[l] = ops.mlstm_step(qd[l, :, :, t], kd[l, :, :, t], vd[l, :, :, t], idv[l, :, :, t], fd[l, :, :, t],
+                                              states[l], state_settled=True)
+                hs[l][:, :, t] = h
+
+    states = [tuple(dev(a) for a in st) for st in st0]
+    hs = [torch.empty(B, NH, T, dv, device="cuda") for _ in range(LAYERS)]
+    run(states, hs)
+    for l in range(LAYERS):
+        assert relerr(host(hs[l]), ref[l][0]) < FP32_TOL
+        for got, want in zip(states[l], ref[l][1]):
+            assert relerr(host(got), want) < FP32_TOL
+
+    # the same launches as one CUDA graph (the decode loop's form): bit-identical to the eager run
+    states_g = [tuple(dev(a) for a in st) for st in st0]
+    hs_g = [torch.empty(B, NH, T, dv, device="cuda") for _ in range(LAYERS)]
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    final = []
+    with torch.cuda.graph(graph, stream=side):
+        work = list(states_g)
+        run(work, hs_g)
+        final = work
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    for l in range(LAYERS):
+        assert torch.equal(hs_g[l], hs[l])
+        for got, want in zip(final[l], states[l]):
+            assert torch.equal(got, want)
+
+    # one state stepped T times back to back, no promise: every launch reads what the one before it wrote
+    st = tuple(dev(a) for a in st0[0])
+    out = []
+    for t in range(T):
+        h, st = ops.mlstm_step(qd[0, :, :, t], kd[0, :, :, t], vd[0, :, :, t], idv[0, :, :, t], fd[0, :, :, t], st, inplace=True)
+        out.append(h)
+    assert relerr(host(torch.stack(out, 2)), ref[0][0]) < FP32_TOL
+
+
 # ---- chunkwise -------------------------------------------------------------------
 def test_chunkwise_config1_fp32(ops, golden):
     g = golden("mlstm_c1_fp32")

@@ -71,4 +71,29 @@ __device__ __forceinline__ void stg_stream(float *p, float4 v) {
 
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? XLSTM_OK : XLSTM_ERR_CUDA; }
 
+// ---- programmatic dependent launch ---------------------------------------------------
+// A kernel launched with launch_overlapped() may become resident while the kernel before it in the stream is
+// still draining.  Inside such a kernel everything BEFORE grid_dependency_wait() may only read memory that the
+// preceding kernel does not write (weights, a state written by an earlier launch); the wait returns once that
+// kernel has completed and its writes are visible.  allow_dependents() is issued right AFTER the wait, so the
+// pre-wait part of launch k+1 can only ever overlap launch k, never anything older.  Both instructions do
+// nothing in a kernel launched the ordinary way, or after a stream operation that is not such a kernel.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline int launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...) == cudaSuccess ? launch_status() : XLSTM_ERR_CUDA;
+}
+
 }  // namespace xl

@@ -6,6 +6,9 @@
 //   prologue  RMSNorm of x (every CTA recomputes the 1/rms of the few rows: 8 KB from L2),
 //   epilogue  + bias, + residual (the block's residual stream), or silu(gate) * up when W holds the two
 //             FFN up projections (gate rows first): the SwiGLU gate without the [M, 2F] intermediate.
+// The weights are the one operand the kernel before this one cannot have written, so every warp asks L2 for the
+// head of its first weight row BEFORE it waits for that kernel (programmatic dependent launch): in a decode loop
+// the weight stream of layer i+1 starts under the tail of layer i and the norm prologue, at no cost in registers.
 #include "common.cuh"
 
 namespace xl {
@@ -94,6 +97,18 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const __nv_bfloat16 *_
     __shared__ float s_part[M][GV_THREADS / 32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nvec = K >> 3;
+    const int total_warps = gridDim.x * (GV_THREADS / 32);
+    const int n_first = blockIdx.x * (GV_THREADS / 32) + warp;
+
+    // ---- L2 prefetch of the head of this warp's first weight row (4 KB: what the first loads will ask for; more
+    //      would only push the running kernel's lines out of L2), then the wait for the preceding kernel
+    if (n_first < N) {
+        const char *row = reinterpret_cast<const char *>(W + (size_t)n_first * K);
+        const int head = K * 2 < 4096 ? K * 2 : 4096;
+        if (lane * 128 < head) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + lane * 128));
+    }
+    grid_dependency_wait();
+    allow_dependents();
 
     // ---- x into shared memory, normalised on the way when a norm weight is given
     if (norm_w) {
@@ -144,8 +159,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const __nv_bfloat16 *_
     }
 
     // ---- one warp per output row (per gate/up pair for the SwiGLU epilogue), rows by grid stride
-    const int total_warps = gridDim.x * (GV_THREADS / 32);
-    for (int n = blockIdx.x * (GV_THREADS / 32) + warp; n < N; n += total_warps) {
+    for (int n = n_first; n < N; n += total_warps) {
         float acc[M];
         row_dot<M>(W + (size_t)n * K, sx, K, lane, acc);
         if (EPI == 2) {
@@ -185,10 +199,10 @@ int gemv_launch(const void *W, const void *x, const void *bias, const void *norm
     // rows are spread over all SMs: enough CTAs of 8 warps for one row per warp, at most 8 CTAs per SM
     const int want = (N + GV_THREADS / 32 - 1) / (GV_THREADS / 32);
     const int grid = want < 148 * 8 ? want : 148 * 8;
-    kern<<<grid, GV_THREADS, smem, st>>>(static_cast<const __nv_bfloat16 *>(W), static_cast<const __nv_bfloat16 *>(x),
-                                         static_cast<const __nv_bfloat16 *>(bias), static_cast<const __nv_bfloat16 *>(norm_w),
-                                         eps, static_cast<const __nv_bfloat16 *>(residual), static_cast<__nv_bfloat16 *>(y), N, K);
-    return launch_status();
+    return launch_overlapped(kern, dim3(grid), dim3(GV_THREADS), smem, st, static_cast<const __nv_bfloat16 *>(W),
+                             static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(bias),
+                             static_cast<const __nv_bfloat16 *>(norm_w), eps, static_cast<const __nv_bfloat16 *>(residual),
+                             static_cast<__nv_bfloat16 *>(y), N, K);
 }
 
 template <int M>

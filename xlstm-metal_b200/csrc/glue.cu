@@ -62,6 +62,15 @@ template <typename T> __device__ __forceinline__ float silu_t(float x) {
     return x / (1.0f + expf(-x));
 }
 
+// 16-byte asynchronous copies global -> shared memory; a thread that only ever reads back the slots it filled
+// itself needs no barrier, only the wait on its own copy groups
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 :: "r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
 // ---------------------------------------------------------------------------
 // RMSNorm: one CTA per row, the row cached in registers (NV 16-byte vectors per thread)
 // ---------------------------------------------------------------------------
@@ -209,6 +218,100 @@ __global__ void __launch_bounds__(RW_WARPS * 32) rms_norm_warp_kernel(const T *_
     }
 }
 
+// Residual add + RMSNorm over many rows, as a stream: one warp per row, 8 warps per CTA, one CTA per SM.  The two
+// input rows (x and the residual) arrive through a ring of RS_RING chunks per warp in shared memory, a chunk being
+// one 16-byte vector of x and one of r per lane (1 KB per warp), filled by cp.async RS_RING chunks ahead - across
+// row boundaries - so 192 KB per SM are in flight whatever the registers do.  The sum s = x + r is rounded to the
+// activation type, stored as the new residual stream and kept packed in registers for the second pass.
+constexpr int RS_WARPS = 8, RS_RING = 24;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(RS_WARPS * 32, 1) add_rms_norm_stream_kernel(const T *__restrict__ x, const T *__restrict__ r,
+                                                                              const T *__restrict__ w, T *__restrict__ sum,
+                                                                              T *__restrict__ y, int64_t rows, int cols,
+                                                                              float eps) {
+    constexpr int VN = Vec16<T>::N;
+    constexpr int NT = RS_WARPS * 32;
+    extern __shared__ __align__(16) unsigned char rs_smem[];
+    uint4 *ring = reinterpret_cast<uint4 *>(rs_smem);          // [RS_RING][2][NT]
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int nvec = cols / VN;
+    const int64_t row0 = (int64_t)blockIdx.x * RS_WARPS + (tid >> 5), rstride = (int64_t)gridDim.x * RS_WARPS;
+    if (row0 >= rows) return;                                   // no CTA barrier below
+    const int my_rows = (int)((rows - row0 + rstride - 1) / rstride);
+    // the copy stream runs RS_RING chunks ahead of the compute loop: (a_row, a_i) is the chunk it issues next
+    int a_k = 0, a_i = 0;
+    size_t a_off = (size_t)row0 * cols;
+    auto issue = [&](int slot) {
+        if (a_k < my_rows) {
+            const int iv = lane + 32 * a_i;
+            if (iv < nvec) {
+                cp_async16(ring + (size_t)(slot * 2 + 0) * NT + tid, x + a_off + (size_t)iv * VN);
+                cp_async16(ring + (size_t)(slot * 2 + 1) * NT + tid, r + a_off + (size_t)iv * VN);
+            }
+            if (++a_i == NV) {
+                a_i = 0;
+                ++a_k;
+                a_off += (size_t)rstride * cols;
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll 1
+    for (int c = 0; c < RS_RING; ++c) issue(c);
+    int slot = 0;
+    for (int k = 0; k < my_rows; ++k) {
+        const size_t off = ((size_t)row0 + (size_t)k * rstride) * cols;
+        uint4 keep[NV];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            cp_async_wait<RS_RING - 1>();                       // the oldest chunk in flight has landed
+            const int iv = lane + 32 * i;
+            if (iv < nvec) {
+                float a[VN], b[VN];
+                unpack16<T>(ring[(size_t)(slot * 2 + 0) * NT + tid], a);
+                unpack16<T>(ring[(size_t)(slot * 2 + 1) * NT + tid], b);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) a[e] += b[e];
+                st16<T>(reinterpret_cast<T *>(&keep[i]), a);
+                *reinterpret_cast<uint4 *>(sum + off + (size_t)iv * VN) = keep[i];
+                unpack16<T>(keep[i], a);                        // the norm is taken of the rounded sum
+#pragma unroll
+                for (int e = 0; e < VN; ++e) ss = fmaf(a[e], a[e], ss);
+            }
+            issue(slot);                                        // refill the slot just consumed
+            slot = slot + 1 == RS_RING ? 0 : slot + 1;
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)cols + eps);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int iv = lane + 32 * i;
+            if (iv < nvec) {
+                float a[VN], wv[VN];
+                unpack16<T>(keep[i], a);
+                if (w) ld16<T>(w + (size_t)iv * VN, wv);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) a[e] = a[e] * inv * (w ? wv[e] : 1.0f);
+                st16<T>(y + off + (size_t)iv * VN, a);
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <typename T, int NV>
+static int add_rms_norm_stream_launch(const T *xp, const T *rp, const T *wp, T *sp, T *yp, int64_t rows, int cols, float eps,
+                                      cudaStream_t st) {
+    auto kern = add_rms_norm_stream_kernel<T, NV>;
+    const size_t smem = (size_t)RS_RING * 2 * RS_WARPS * 32 * sizeof(uint4);
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return XLSTM_ERR_CUDA;
+    const int64_t want = (rows + RS_WARPS - 1) / RS_WARPS;
+    kern<<<(unsigned)(want < 148 ? want : 148), RS_WARPS * 32, smem, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
+    return launch_status();
+}
+
 template <typename T>
 static int rms_norm_launch(const void *x, const void *r, const void *w, void *sum, void *y, int64_t rows, int cols,
                            float eps, cudaStream_t st) {
@@ -220,8 +323,12 @@ static int rms_norm_launch(const void *x, const void *r, const void *w, void *su
                          cols % VN == 0;
     const int nvec = cols / VN;
     const dim3 grid((unsigned)rows);
-    if (aligned && !r && rows >= 4 * 148 && nvec <= 32 * 16) {   // enough rows to give every SM several warps' worth; the
-        // residual variant stays on the CTA-per-row kernel, which measured faster for two input streams
+    if (aligned && r && rows >= 8 * 148 && nvec <= 32 * 16) {    // two input streams, many rows: the streamed kernel
+        if (nvec <= 32 * 4) return add_rms_norm_stream_launch<T, 4>(xp, rp, wp, sp, yp, rows, cols, eps, st);
+        if (nvec <= 32 * 8) return add_rms_norm_stream_launch<T, 8>(xp, rp, wp, sp, yp, rows, cols, eps, st);
+        return add_rms_norm_stream_launch<T, 16>(xp, rp, wp, sp, yp, rows, cols, eps, st);
+    }
+    if (aligned && !r && rows >= 4 * 148 && nvec <= 32 * 16) {   // enough rows to give every SM several warps' worth
         const int64_t want = (rows + RW_WARPS - 1) / RW_WARPS;
         const unsigned wg = (unsigned)(want < 148 * 8 ? want : 148 * 8);
         if (nvec <= 32 * 4) rms_norm_warp_kernel<T, 4><<<wg, RW_WARPS * 32, 0, st>>>(xp, rp, wp, sp, yp, rows, cols, eps);
@@ -242,51 +349,112 @@ static int rms_norm_launch(const void *x, const void *r, const void *w, void *su
 // ---------------------------------------------------------------------------
 constexpr int OG_WARPS = 8;
 
+__device__ __forceinline__ uint4 ldg16_raw(const void *p) { return *reinterpret_cast<const uint4 *>(p); }
+
+// sigmoid for the output gate: bf16 outputs take it from ONE special-function op (tanh.approx, relative error
+// 2^-11, below the bf16 rounding), fp32 outputs the exact form
+template <typename T> __device__ __forceinline__ float og_sigmoid(float x) {
+    if (sizeof(T) == 2) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+        return fmaf(0.5f, t, 0.5f);
+    }
+    return 1.0f / (1.0f + expf(-x));
+}
+
+// The warps of the grid walk the rows; a warp holds its row (h and the gate pre-activations) as packed 16-byte
+// vectors and has the NEXT row's loads in flight while it reduces, scales and stores the current one.  The row
+// stride of the grid is a multiple of NH (the launcher sees to it), so a warp stays on one head and its
+// (batch, token) position advances by additions: no division in the loop.
 template <typename T, int NV>
 __global__ void __launch_bounds__(OG_WARPS * 32) mlstm_output_gate_kernel(
     const T *__restrict__ h, const T *__restrict__ og, const T *__restrict__ w, T *__restrict__ y, int64_t rows, int NH,
     int S, int dv, int64_t hsb, int64_t hsh, int64_t hss, int64_t ldo, float eps) {
     constexpr int VN = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
-    // row = (b * S + s) * NH + head; the warps of the grid walk the rows
-    for (int64_t row = (int64_t)blockIdx.x * OG_WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * OG_WARPS) {
-    const int head = (int)(row % NH);
-    const int64_t bs = row / NH;
-    const int64_t b = bs / S, s = bs % S;
-    const T *hr = h + b * hsb + head * hsh + s * hss;
     const int nvec = dv / VN;
-    const T *ogr = og + bs * ldo + (size_t)head * dv;
-    const T *wr = w ? w + (size_t)head * dv : nullptr;
-    T *yr = y + row * dv;
-    // all loads of the row (h and the gate pre-activations) are issued before the reduction
-    float v[NV][VN], o[NV][VN];
+    const int64_t stride = (int64_t)gridDim.x * OG_WARPS;      // rows between two rows of a warp: k * NH
+    int64_t row = (int64_t)blockIdx.x * OG_WARPS + (threadIdx.x >> 5);
+    grid_dependency_wait();   // h and the gate pre-activations come from the kernels before this one
+    allow_dependents();
+    if (row >= rows) return;
+    // row = (b * S + s) * NH + head
+    const int head = (int)(row % NH);
+    int64_t bs = row / NH;                                     // b * S + s
+    const int64_t bs_step = stride / NH;
+    int64_t b = bs / S;
+    int s = (int)(bs % S);
+    const int64_t b_step = bs_step / S;
+    const int s_step = (int)(bs_step % S);
+    const T *hbase = h + head * hsh;
+    const T *ogbase = og + (size_t)head * dv;
+
+    auto load_row = [&](int64_t b_, int s_, int64_t bs_, uint4 (&hv)[NV], uint4 (&ov)[NV]) {
+        const T *hr = hbase + b_ * hsb + s_ * hss;
+        const T *ogr = ogbase + bs_ * ldo;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int iv = lane + i * 32;
+            if (iv < nvec) {
+                hv[i] = ldg16_raw(hr + (size_t)iv * VN);
+                ov[i] = ldg16_raw(ogr + (size_t)iv * VN);
+            }
+        }
+    };
+    // the norm weight of the head, unpacked once
+    float wf[NV][VN];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int iv = lane + i * 32;
-        if (iv < nvec) {
-            ld16<T>(hr + (size_t)iv * VN, v[i]);
-            ld16<T>(ogr + (size_t)iv * VN, o[i]);
-        }
+        if (w && iv < nvec) unpack16<T>(ldg16_raw(w + (size_t)head * dv + (size_t)iv * VN), wf[i]);
+        else
+#pragma unroll
+            for (int e = 0; e < VN; ++e) wf[i][e] = 1.0f;
     }
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < NV; ++i)
-        if (lane + i * 32 < nvec)
-#pragma unroll
-            for (int e = 0; e < VN; ++e) ss += v[i][e] * v[i][e];
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int iv = lane + i * 32;
-        if (iv < nvec) {
-            float wv[VN];
-            if (wr) ld16<T>(wr + (size_t)iv * VN, wv);
-#pragma unroll
-            for (int e = 0; e < VN; ++e) v[i][e] = v[i][e] * inv * (wr ? wv[e] : 1.0f) * sigmoid_t<T>(o[i][e]);
-            st16<T>(yr + (size_t)iv * VN, v[i]);
+
+    uint4 hv[NV], ov[NV];
+    load_row(b, s, bs, hv, ov);
+    for (; row < rows; row += stride) {
+        // position of this warp's next row
+        int64_t bn = b + b_step, bsn = bs + bs_step;
+        int sn = s + s_step;
+        if (sn >= S) {
+            sn -= S;
+            ++bn;
         }
-    }
+        uint4 hn[NV], on[NV];
+        if (row + stride < rows) load_row(bn, sn, bsn, hn, on);
+        float v[NV][VN];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (lane + i * 32 < nvec) {
+                unpack16<T>(hv[i], v[i]);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) ss = fmaf(v[i][e], v[i][e], ss);
+            }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+        T *yr = y + row * dv;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int iv = lane + i * 32;
+            if (iv < nvec) {
+                float o[VN];
+                unpack16<T>(ov[i], o);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) v[i][e] = v[i][e] * inv * wf[i][e] * og_sigmoid<T>(o[e]);
+                st16<T>(yr + (size_t)iv * VN, v[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            hv[i] = hn[i];
+            ov[i] = on[i];
+        }
+        b = bn;
+        s = sn;
+        bs = bsn;
     }
 }
 
@@ -296,16 +464,20 @@ static int output_gate_launch(const void *h, const void *og, const void *w, void
     constexpr int VN = Vec16<T>::N;
     const int nvec = dv / VN;
     const int64_t rows = (int64_t)B * S * NH;
+    // enough CTAs to fill the GPU, rounded up so that the grid's row stride (grid * OG_WARPS) is a multiple of NH:
+    // a warp then stays on one head
     const int64_t want = (rows + OG_WARPS - 1) / OG_WARPS;
-    const unsigned grid = (unsigned)(want < 148 * 8 ? want : 148 * 8);
+    int64_t cap = 148 * 8;
+    while ((cap * OG_WARPS) % NH) ++cap;
+    const unsigned grid = (unsigned)(want < cap ? want : cap);
     const T *hp = static_cast<const T *>(h), *op = static_cast<const T *>(og), *wp = static_cast<const T *>(w);
     T *yp = static_cast<T *>(y);
-    if (nvec <= 32) mlstm_output_gate_kernel<T, 1><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
-    else if (nvec <= 64) mlstm_output_gate_kernel<T, 2><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
-    else if (nvec <= 128) mlstm_output_gate_kernel<T, 4><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
-    else if (nvec <= 256) mlstm_output_gate_kernel<T, 8><<<grid, OG_WARPS * 32, 0, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
-    else return XLSTM_ERR_UNSUPPORTED;
-    return launch_status();
+    const dim3 g(grid), blk(OG_WARPS * 32);
+    if (nvec <= 32) return launch_overlapped(mlstm_output_gate_kernel<T, 1>, g, blk, 0, st, hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    if (nvec <= 64) return launch_overlapped(mlstm_output_gate_kernel<T, 2>, g, blk, 0, st, hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    if (nvec <= 128) return launch_overlapped(mlstm_output_gate_kernel<T, 4>, g, blk, 0, st, hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    if (nvec <= 256) return launch_overlapped(mlstm_output_gate_kernel<T, 8>, g, blk, 0, st, hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    return XLSTM_ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------------------
@@ -373,58 +545,66 @@ static int swiglu_launch(const void *g, const void *u, void *y, int64_t rows, in
 }
 
 // ---------------------------------------------------------------------------
-// causal depthwise conv1d (+ SiLU), channels-last.  A thread owns VN adjacent channels and CONV_G
-// consecutive tokens: it issues the CONV_G + K - 1 input loads it needs at once (the K - 1 halo rows are
-// L1 hits: the neighbouring warp of the CTA loads them as its own rows), then computes its outputs; no
-// loop-carried window, so many independent loads are in flight per thread.  A warp covers 32*VN adjacent
-// channels, the four warps of a CTA four consecutive token groups (CONV_T = 32 tokens per CTA).
+// causal depthwise conv1d (+ SiLU), channels-last.  A thread owns VN adjacent channels and a run of consecutive
+// tokens.  Its input rows arrive through a private ring of CONV_RING 16-byte slots in shared memory filled by
+// cp.async, so CONV_RING rows per thread are in flight without costing registers, and the window of the last
+// K - 1 inputs is carried in registers, so only the first token of a run re-reads its K - 1 halo rows.  A warp
+// covers 32*VN adjacent channels (one 512-byte piece of a row), the four warps of a CTA four consecutive runs.
+// Every slot is written and read by the same thread: no barrier in the loop.
 // ---------------------------------------------------------------------------
-constexpr int CONV_G = 8;           // tokens per thread
-constexpr int CONV_T = 32;          // tokens per CTA (4 warps x CONV_G)
+constexpr int CONV_RING = 16;       // input rows in flight per thread
+constexpr int CONV_MIN_RUN = 8;     // tokens per thread: at least / at most
+constexpr int CONV_MAX_RUN = 128;
 constexpr int CONV_ALIAS_MAX = 16;  // longest call whose new state may overwrite the old one in place (one CTA per batch row)
 constexpr int CONV_KMAX = 8;
 
+
+// SiLU for the convolution output: bf16 results take the sigmoid from one tanh.approx
+template <typename T> __device__ __forceinline__ float conv_silu(float x) {
+    if (sizeof(T) == 2) {
+        float t;
+        const float hx = 0.5f * x;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(hx));
+        return fmaf(hx, t, hx);
+    }
+    return x / (1.0f + expf(-x));
+}
+
 template <typename T, int K>
-__global__ void __launch_bounds__(128) causal_conv1d_kernel(const T *__restrict__ x, const T *__restrict__ w,
-                                                            const T *__restrict__ bias, const T *__restrict__ state_in,
-                                                            T *__restrict__ state_out, T *__restrict__ y, int S, int C,
-                                                            int act_silu) {
+__global__ void __launch_bounds__(128, (K * (16 / sizeof(T)) <= 40) ? 4 : 2) causal_conv1d_kernel(const T *__restrict__ x, const T *__restrict__ w,
+                                                               const T *__restrict__ bias, const T *__restrict__ state_in,
+                                                               T *__restrict__ state_out, T *__restrict__ y, int S, int C,
+                                                               int act_silu, int run) {
     constexpr int VN = Vec16<T>::N;
     constexpr int H = K - 1;                               // history length
-    constexpr int NIN = CONV_G + H;                        // input rows a thread reads
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ uint4 ring[CONV_RING][128];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cv = blockIdx.x * 32 + lane;                 // channel vector
     const bool ch_ok = cv * VN < C;
     const int c0 = ch_ok ? cv * VN : 0;
     const int b = blockIdx.z;
-    const int s0 = blockIdx.y * CONV_T + warp * CONV_G;    // first token of this thread
+    const int cta_tokens = 4 * run;
+    const int s_begin = blockIdx.y * cta_tokens + warp * run;
+    const int n_tok = ch_ok ? min(run, S - s_begin) : 0;   // tokens of this thread (<= 0: none)
     const T *xb = x + (size_t)b * S * C + c0;
     T *yb = y + (size_t)b * S * C + c0;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    // input rows s0 - H .. s0 + CONV_G - 1; rows before token 0 come from the state (or are zero)
-    uint4 raw[NIN];
+    // the first CONV_RING rows of the run go out at once (one group per row, empty groups past the end)
 #pragma unroll
-    for (int r = 0; r < NIN; ++r) {
-        const int t = s0 - H + r;
-        if (!ch_ok || t >= S) raw[r] = zero4;
-        else if (t >= 0) raw[r] = *reinterpret_cast<const uint4 *>(xb + (size_t)t * C);
-        else if (state_in) raw[r] = *reinterpret_cast<const uint4 *>(state_in + ((size_t)b * H + (H + t)) * C + c0);
-        else raw[r] = zero4;
+    for (int r = 0; r < CONV_RING; ++r) {
+        if (r < n_tok) cp_async16(&ring[r][tid], xb + (size_t)(s_begin + r) * C);
+        cp_async_commit();
     }
-    // the new state = last K-1 inputs of [state ; x]: written by the CTA that owns the last token, after
-    // every warp of it has read what it needs from the old state (in-place update)
-    const bool owns_state = state_out != nullptr && (int)blockIdx.y == (S - 1) / CONV_T;
-    uint4 st_new[H > 0 ? H : 1];
-    if (owns_state && warp == 0 && ch_ok) {
+    // rows before token 0 come from the state (or are zero)
+    auto load_old = [&](int t) -> uint4 {
+        if (t >= 0) return *reinterpret_cast<const uint4 *>(xb + (size_t)t * C);
+        if (state_in) return *reinterpret_cast<const uint4 *>(state_in + ((size_t)b * H + (H + t)) * C + c0);
+        return zero4;
+    };
+    if (n_tok > 0) {
+        uint4 hist[H > 0 ? H : 1];
 #pragma unroll
-        for (int j = 0; j < H; ++j) {
-            const int t = S - H + j;                        // token held by state slot j
-            if (t >= 0) st_new[j] = *reinterpret_cast<const uint4 *>(xb + (size_t)t * C);
-            else if (state_in) st_new[j] = *reinterpret_cast<const uint4 *>(state_in + ((size_t)b * H + (j + S)) * C + c0);
-            else st_new[j] = zero4;
-        }
-    }
-    if (ch_ok) {
+        for (int j = 0; j < H; ++j) hist[j] = load_old(s_begin - H + j);
         // the VN x K taps of this thread's channels are VN*K contiguous elements = K 16-byte vectors
         float wflat[VN * K];
 #pragma unroll
@@ -439,36 +619,46 @@ __global__ void __launch_bounds__(128) causal_conv1d_kernel(const T *__restrict_
         else
 #pragma unroll
             for (int e = 0; e < VN; ++e) bv[e] = 0.f;
-        // every input row is unpacked once into a window of the last K rows (fully unrolled: the shifts
-        // below are register renames)
+        // window of the last K rows, unpacked once each, as a ring of K register rows: at step u of an unrolled
+        // block of K steps the newest row sits in slot u and tap j reads slot (u + 1 + j) % K
         float win[K][VN];
 #pragma unroll
-        for (int j = 0; j < H; ++j) unpack16<T>(raw[j], win[j]);
+        for (int j = 0; j < H; ++j) unpack16<T>(hist[j], win[j + 1]);
+        for (int i0 = 0; i0 < n_tok; i0 += K) {
 #pragma unroll
-        for (int g = 0; g < CONV_G; ++g) {
-            unpack16<T>(raw[g + H], win[H]);
-            if (s0 + g < S) {
-                float acc[VN];
+            for (int u = 0; u < K; ++u) {
+                const int i = i0 + u;
+                if (i < n_tok) {
+                    cp_async_wait<CONV_RING - 1>();            // the group of row i has landed
+                    const uint4 raw = ring[i % CONV_RING][tid];
+                    unpack16<T>(raw, win[u]);
+                    float acc[VN];
 #pragma unroll
-                for (int e = 0; e < VN; ++e) acc[e] = bv[e];
+                    for (int e = 0; e < VN; ++e) acc[e] = bv[e];
 #pragma unroll
-                for (int j = 0; j < K; ++j)
+                    for (int j = 0; j < K; ++j)
 #pragma unroll
-                    for (int e = 0; e < VN; ++e) acc[e] = fmaf(wk[j][e], win[j][e], acc[e]);
-                if (act_silu)
+                        for (int e = 0; e < VN; ++e) acc[e] = fmaf(wk[j][e], win[(u + 1 + j) % K][e], acc[e]);
+                    if (act_silu)
 #pragma unroll
-                    for (int e = 0; e < VN; ++e) acc[e] = silu_t<T>(acc[e]);
-                st16<T>(yb + (size_t)(s0 + g) * C, acc);
+                        for (int e = 0; e < VN; ++e) acc[e] = conv_silu<T>(acc[e]);
+                    st16<T>(yb + (size_t)(s_begin + i) * C, acc);
+                    // refill the slot just consumed with the row CONV_RING ahead (after its value has been used)
+                    if (i + CONV_RING < n_tok) cp_async16(&ring[i % CONV_RING][tid], xb + (size_t)(s_begin + i + CONV_RING) * C);
+                    cp_async_commit();
+                }
             }
-#pragma unroll
-            for (int j = 0; j < H; ++j)
-#pragma unroll
-                for (int e = 0; e < VN; ++e) win[j][e] = win[j + 1][e];
         }
     }
+    cp_async_wait<0>();
+    // the new state = last K-1 inputs of [state ; x]: written by the CTA that owns the last token, after
+    // every warp of it has read what it needs from the old state (in-place update)
     if (state_out != nullptr) {          // uniform over the CTA
         __syncthreads();
-        if (owns_state && warp == 0 && ch_ok) {
+        if ((int)blockIdx.y == (S - 1) / cta_tokens && warp == 0 && ch_ok) {
+            uint4 st_new[H > 0 ? H : 1];
+#pragma unroll
+            for (int j = 0; j < H; ++j) st_new[j] = load_old(S - H + j);
 #pragma unroll
             for (int j = 0; j < H; ++j) *reinterpret_cast<uint4 *>(state_out + ((size_t)b * H + j) * C + c0) = st_new[j];
         }
@@ -546,22 +736,27 @@ extern "C" int xlstm_causal_conv1d(const void *x, const void *w, const void *bia
     const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(bias) |
                          reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out) |
                          reinterpret_cast<uintptr_t>(w);
-    if (C % vn || (al & 15u) || B > 65535 || (S + CONV_T - 1) / CONV_T > 65535) return XLSTM_ERR_UNSUPPORTED;
+    if (C % vn || (al & 15u) || B > 65535) return XLSTM_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int cvec = C / vn;
-    const dim3 grid((cvec + 31) / 32, (S + CONV_T - 1) / CONV_T, B);
+    // tokens per thread: the longest run (fewest halo re-reads) that still gives every SM four CTAs
+    int run = CONV_MAX_RUN;
+    while (run > CONV_MIN_RUN && (int64_t)((cvec + 31) / 32) * ((S + 4 * run - 1) / (4 * run)) * B < 148 * 4) run >>= 1;
+    const int cta_tokens = 4 * run;
+    if ((S + cta_tokens - 1) / cta_tokens > 65535) return XLSTM_ERR_UNSUPPORTED;
+    const dim3 grid((cvec + 31) / 32, (S + cta_tokens - 1) / cta_tokens, B);
 #define XL_CONV_CASE(KK)                                                                                              \
     case KK:                                                                                                          \
         if (dtype == XLSTM_F32)                                                                                       \
             causal_conv1d_kernel<float, KK><<<grid, 128, 0, st>>>(                                                    \
                 static_cast<const float *>(x), static_cast<const float *>(w), static_cast<const float *>(bias),      \
                 static_cast<const float *>(state_in), static_cast<float *>(state_out), static_cast<float *>(y), S, C, \
-                act_silu);                                                                                            \
+                act_silu, run);                                                                                       \
         else                                                                                                          \
             causal_conv1d_kernel<__nv_bfloat16, KK><<<grid, 128, 0, st>>>(                                            \
                 static_cast<const __nv_bfloat16 *>(x), static_cast<const __nv_bfloat16 *>(w),                         \
                 static_cast<const __nv_bfloat16 *>(bias), static_cast<const __nv_bfloat16 *>(state_in),               \
-                static_cast<__nv_bfloat16 *>(state_out), static_cast<__nv_bfloat16 *>(y), S, C, act_silu);            \
+                static_cast<__nv_bfloat16 *>(state_out), static_cast<__nv_bfloat16 *>(y), S, C, act_silu, run);       \
         break;
     switch (K) {
         XL_CONV_CASE(1) XL_CONV_CASE(2) XL_CONV_CASE(3) XL_CONV_CASE(4)

@@ -8,6 +8,10 @@
 // walked in batches of UNROLL independent 128-bit streaming loads per thread,
 // the first batch issued before the gate prologue and each next batch before
 // the current one is consumed, to keep enough bytes in flight for HBM3e.
+// The kernel is launched so that its CTAs may become resident under the tail of the kernel before it; when the
+// caller promises that the state it reads was written by an earlier launch than that one (decode over a stack
+// of layers: the kernel before a layer's step is that layer's projection), the first batch of state loads goes
+// out before the wait on that kernel, so the HBM stream does not stop at the kernel boundary.
 #include "common.cuh"
 
 namespace xl {
@@ -21,7 +25,7 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
                   const T *__restrict__ ig, const T *__restrict__ fg,
                   const float *C0, const float *__restrict__ n0, const float *__restrict__ m0,
                   T *__restrict__ h, float *C1, float *__restrict__ n1, float *__restrict__ m1,
-                  int dqk, int dv, float eps, float qscale, float gate_cap) {
+                  int dqk, int dv, float eps, float qscale, float gate_cap, int state_settled) {
     constexpr int CV = DVT / 4;       // 128-bit column vectors per row of the tile
     constexpr int RG = THREADS / CV;  // row groups walking the rows in parallel
     extern __shared__ float smem[];
@@ -42,12 +46,24 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
     float *Cout = C1 + (size_t)bh * dqk * dv + col;
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
-    // first batch of state rows: in flight while the prologue below runs
+    // first batch of state rows: in flight while the prologue below runs (and, for a settled state, while the
+    // preceding kernel drains)
     float4 c[UNROLL];
+    if (state_settled) {
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-        const int j = rg + u * RG;
-        c[u] = (active && has_state && j < dqk) ? ldg_stream(Cin + (size_t)j * dv) : zero4;
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = rg + u * RG;
+            c[u] = (active && has_state && j < dqk) ? ldg_stream(Cin + (size_t)j * dv) : zero4;
+        }
+    }
+    grid_dependency_wait();
+    allow_dependents();
+    if (!state_settled) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = rg + u * RG;
+            c[u] = (active && has_state && j < dqk) ? ldg_stream(Cin + (size_t)j * dv) : zero4;
+        }
     }
 
     // stabilised gates (every thread: two exps and a log1p are cheaper than a broadcast)
@@ -125,7 +141,8 @@ mlstm_step_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__r
 template <typename T>
 static int mlstm_step_launch(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                              const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
-                             float *m1, int BH, int dqk, int dv, float eps, float gate_cap, cudaStream_t st) {
+                             float *m1, int BH, int dqk, int dv, float eps, float gate_cap, int state_settled,
+                             cudaStream_t st) {
     constexpr int DVT = STEP_DVT, THREADS = STEP_THREADS, UNROLL = STEP_UNROLL;
     dim3 grid(BH, (dv + DVT - 1) / DVT);
     size_t smem = sizeof(float) * (2 * (size_t)dqk + (THREADS / (DVT / 4)) * DVT);
@@ -135,19 +152,18 @@ static int mlstm_step_launch(const void *q, const void *k, const void *v, const 
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return XLSTM_ERR_CUDA;
     }
-    kern<<<grid, THREADS, smem, st>>>(static_cast<const T *>(q), static_cast<const T *>(k),
-                                      static_cast<const T *>(v), static_cast<const T *>(ig),
-                                      static_cast<const T *>(fg), C0, n0, m0, static_cast<T *>(h), C1, n1, m1,
-                                      dqk, dv, eps, 1.0f / sqrtf((float)dqk), gate_cap);
-    return launch_status();
+    return launch_overlapped(kern, grid, dim3(THREADS), smem, st, static_cast<const T *>(q), static_cast<const T *>(k),
+                             static_cast<const T *>(v), static_cast<const T *>(ig), static_cast<const T *>(fg), C0, n0, m0,
+                             static_cast<T *>(h), C1, n1, m1, dqk, dv, eps, 1.0f / sqrtf((float)dqk), gate_cap,
+                             state_settled);
 }
 
 }  // namespace xl
 
 static int mlstm_step_checked(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                               const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
-                              float *m1, int B, int NH, int dqk, int dv, float eps, float gate_cap, int dtype,
-                              void *stream) {
+                              float *m1, int B, int NH, int dqk, int dv, float eps, float gate_cap, int flags,
+                              int dtype, void *stream) {
     if (!q || !k || !v || !ig || !fg || !h || !C1 || !n1 || !m1) return XLSTM_ERR_INVALID;
     if (B <= 0 || NH <= 0 || dqk <= 0 || dv <= 0) return XLSTM_ERR_INVALID;
     if (C0 && (!n0 || !m0)) return XLSTM_ERR_INVALID;
@@ -155,21 +171,32 @@ static int mlstm_step_checked(const void *q, const void *k, const void *v, const
     if (dv % 4 != 0) return XLSTM_ERR_UNSUPPORTED;
     if (dtype != XLSTM_F32 && dtype != XLSTM_BF16) return XLSTM_ERR_UNSUPPORTED;
     if ((int64_t)B * NH > 2147483647LL || (dv + xl::STEP_DVT - 1) / xl::STEP_DVT > 65535) return XLSTM_ERR_UNSUPPORTED;
+    if (flags & ~XLSTM_STEP_STATE_SETTLED) return XLSTM_ERR_INVALID;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int settled = (flags & XLSTM_STEP_STATE_SETTLED) ? 1 : 0;
     if (dtype == XLSTM_F32)
-        return xl::mlstm_step_launch<float>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, gate_cap, st);
-    return xl::mlstm_step_launch<__nv_bfloat16>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, gate_cap, st);
+        return xl::mlstm_step_launch<float>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, gate_cap,
+                                            settled, st);
+    return xl::mlstm_step_launch<__nv_bfloat16>(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B * NH, dqk, dv, eps, gate_cap,
+                                                settled, st);
 }
 
 extern "C" int xlstm_mlstm_step(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                                 const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
                                 float *m1, int B, int NH, int dqk, int dv, float eps, int dtype, void *stream) {
-    return mlstm_step_checked(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, dqk, dv, eps, 0.0f, dtype, stream);
+    return mlstm_step_checked(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, dqk, dv, eps, 0.0f, 0, dtype, stream);
 }
 
 extern "C" int xlstm_mlstm_step_gatecap(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                                         const float *C0, const float *n0, const float *m0, void *h, float *C1,
                                         float *n1, float *m1, int B, int NH, int dqk, int dv, float eps, float gate_cap,
                                         int dtype, void *stream) {
-    return mlstm_step_checked(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, dqk, dv, eps, gate_cap, dtype, stream);
+    return mlstm_step_checked(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, dqk, dv, eps, gate_cap, 0, dtype, stream);
+}
+
+extern "C" int xlstm_mlstm_step_ex(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                                   const float *C0, const float *n0, const float *m0, void *h, float *C1, float *n1,
+                                   float *m1, int B, int NH, int dqk, int dv, float eps, float gate_cap, int flags,
+                                   int dtype, void *stream) {
+    return mlstm_step_checked(q, k, v, ig, fg, C0, n0, m0, h, C1, n1, m1, B, NH, dqk, dv, eps, gate_cap, flags, dtype, stream);
 }

@@ -12,6 +12,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libxlstm_cuda.so"
 
 F32, BF16 = 0, 1
+STEP_STATE_SETTLED = 1
 
 _SIGNATURES = {
     "xlstm_version": (c_int, []),
@@ -37,6 +38,8 @@ _SIGNATURES = {
     "xlstm_slstm_recurrent": (c_int, [c_void_p] * 3 + [c_void_p] * 4 + [c_void_p] * 5 + [c_int] * 4 + [c_float, c_int, c_void_p]),
     "xlstm_mlstm_step_gatecap": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 4
                                  + [c_float, c_float, c_int, c_void_p]),
+    "xlstm_mlstm_step_ex": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 4
+                            + [c_float, c_float, c_int, c_int, c_void_p]),
     "xlstm_mlstm_chunkwise_fwd_gatecap": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6
                                           + [c_float, c_float, c_int, ctypes.POINTER(c_int64), c_void_p, c_size_t, c_void_p]),
     "xlstm_rms_norm": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_float, c_int, c_void_p]),

@@ -364,7 +364,8 @@ class mLSTMBlock(nn.Module):
         q, k, v = y[:, :o_k].view(B, NH, dqk), y[:, o_k:o_v].view(B, NH, dqk), y[:, o_v:o_g].view(B, NH, dv)
         rk = cell.recurrent_kernel
         h, new_state = ops.mlstm_step(q, k, v, y[:, o_g:o_g + NH], y[:, o_g + NH:o_o], state, rk.eps,
-                                      inplace=rk.inplace_state, gate_cap=cell.projection_cell.gate_soft_cap)
+                                      inplace=rk.inplace_state, gate_cap=cell.projection_cell.gate_soft_cap,
+                                      state_settled=True)   # the launch before this one is the projection above
         oc = cell.output_cell
         gated = ops.mlstm_output_gate(h.unsqueeze(2), y[:, o_o:].unsqueeze(1), oc.norm.weight, oc.norm.eps)
         x1 = ops.linear_token(oc.out_proj.weight, gated.reshape(B, -1), bias=oc.out_proj.bias, residual=x2)

@@ -53,12 +53,15 @@ def softcap(x: torch.Tensor, cap: Optional[float], out: Optional[torch.Tensor] =
 
 
 def mlstm_step(q, k, v, i, f, state=None, eps: float = 1e-6, inplace: bool = False,
-               gate_cap: Optional[float] = None):
+               gate_cap: Optional[float] = None, state_settled: bool = False):
     """One decode step.  q,k: [B,NH,dqk]; v: [B,NH,dv]; i,f: [B,NH]; state (C,n,m) fp32 or None.
 
     Returns ``h [B,NH,dv]`` and the new state.  ``inplace=True`` overwrites the
     caller's ``C`` (the 2 x dqk x dv x 4 byte stream then hits one buffer).
     ``gate_cap`` > 0: ``i`` and ``f`` are the raw gate projections and are soft-capped inside the kernel.
+    ``state_settled=True`` promises that ``state`` was not written by the kernel launched just before this call
+    (a layer stack: the launch before a layer's step is its projection); the kernel then starts streaming the
+    state while that kernel drains.
     """
     _need_cuda(q, k, v, i, f)
     B, NH, dqk = q.shape
@@ -76,16 +79,11 @@ def mlstm_step(q, k, v, i, f, state=None, eps: float = 1e-6, inplace: bool = Fal
     C1 = C0 if (inplace and C0 is not None) else torch.empty(B, NH, dqk, dv, dtype=torch.float32, device=dev)
     n1 = torch.empty(B, NH, dqk, dtype=torch.float32, device=dev)
     m1 = torch.empty(B, NH, dtype=torch.float32, device=dev)
-    if gate_cap is not None and gate_cap > 0:
-        _lib.check(_lib.load().xlstm_mlstm_step_gatecap(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
-            h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, dqk, dv, float(eps), float(gate_cap), dt,
-            _stream()), "xlstm_mlstm_step_gatecap")
-        return h, (C1, n1, m1)
-    _lib.check(_lib.load().xlstm_mlstm_step(
+    flags = _lib.STEP_STATE_SETTLED if (state_settled and state is not None) else 0
+    _lib.check(_lib.load().xlstm_mlstm_step_ex(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
-        h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, dqk, dv, float(eps), dt, _stream()),
-        "xlstm_mlstm_step")
+        h.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(), B, NH, dqk, dv, float(eps),
+        float(gate_cap) if gate_cap is not None else 0.0, flags, dt, _stream()), "xlstm_mlstm_step_ex")
     return h, (C1, n1, m1)
 
 

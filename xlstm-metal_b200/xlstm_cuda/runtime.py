@@ -41,9 +41,11 @@ class DecodePipeline:
         return buf
 
     def step(self, packed_host: torch.Tensor, state_in: Tuple[torch.Tensor, ...],
-             state_out: Tuple[torch.Tensor, ...], h_host: torch.Tensor) -> None:
+             state_out: Tuple[torch.Tensor, ...], h_host: torch.Tensor, state_settled: bool = False) -> None:
         """Enqueue one decode step.  ``packed_host`` and ``h_host`` are pinned host tensors;
-        ``state_in`` / ``state_out`` are (C, n, m) fp32 device tensors (different buffers)."""
+        ``state_in`` / ``state_out`` are (C, n, m) fp32 device tensors (different buffers).
+        ``state_settled``: ``state_in`` was not written by the step enqueued just before this one (a stack of
+        layers), so the kernel may start streaming it while that step drains."""
         s = self.t % self.depth
         first_use = self.t < self.depth
         with torch.cuda.stream(self.s_in):
@@ -56,12 +58,13 @@ class DecodePipeline:
             if not first_use:
                 self.s_run.wait_event(self.ev_out[s])     # h slot drained by its device -> host copy
             base = self.stage[s].data_ptr()
-            st = self.lib.xlstm_mlstm_step(
+            st = self.lib.xlstm_mlstm_step_ex(
                 base + self.off[0], base + self.off[1], base + self.off[2], base + self.off[3], base + self.off[4],
                 state_in[0].data_ptr(), state_in[1].data_ptr(), state_in[2].data_ptr(), self.h_dev[s].data_ptr(),
                 state_out[0].data_ptr(), state_out[1].data_ptr(), state_out[2].data_ptr(),
-                self.B, self.NH, self.dqk, self.dv, self.eps, _lib.BF16, self.s_run.cuda_stream)
-            _lib.check(st, "xlstm_mlstm_step")
+                self.B, self.NH, self.dqk, self.dv, self.eps, 0.0, _lib.STEP_STATE_SETTLED if state_settled else 0,
+                _lib.BF16, self.s_run.cuda_stream)
+            _lib.check(st, "xlstm_mlstm_step_ex")
             self.ev_run[s].record(self.s_run)
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(self.ev_run[s])
@@ -82,8 +85,8 @@ class DecodePipeline:
             fork.record(self.s_run)
             self.s_in.wait_event(fork)
             self.s_out.wait_event(fork)
-            for packed_host, state_in, state_out, h_host in steps:
-                self.step(packed_host, state_in, state_out, h_host)
+            for item in steps:
+                self.step(*item)   # (packed_host, state_in, state_out, h_host[, state_settled])
             for side in (self.s_in, self.s_out):
                 join = torch.cuda.Event()
                 join.record(side)
