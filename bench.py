@@ -326,7 +326,7 @@ def run_ours(args):
 
     # ---- end-to-end leg: host buffers through the public host-fed decode API -----------------
     from xlstm_cuda.runtime import DecodePipeline
-    pipe = DecodePipeline(B, NH, DQK, DV, device)
+    pipe = DecodePipeline(B, NH, DQK, DV, device, group=N_LAYERS)   # the steps of one pass over the layer ring travel together
     packed = [pipe.pack(q[s_], k[s_], v[s_], i[s_], f[s_]) for s_ in range(N_INPUT_SETS)]
     h_host = [torch.empty(B, NH, DV, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     side2 = [0] * N_LAYERS

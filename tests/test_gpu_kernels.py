@@ -192,6 +192,60 @@ def test_mlstm_step_layer_ring_overlapped_launches(ops):
     assert relerr(host(torch.stack(out, 2)), ref[0][0]) < FP32_TOL
 
 
+@pytest.mark.parametrize("group", [1, 3])
+def test_decode_pipeline_host_fed(ops, group):
+    """runtime.DecodePipeline: pinned host q,k,v,i,f in, h out, every step; eager enqueue and the captured graph
+    (steps travelling in groups) must both reproduce the plain decode step bit for bit, states included."""
+    from xlstm_cuda.runtime import DecodePipeline
+    B, NH, dqk, dv, LAYERS, T = 2, 4, 128, 256, 3, 4
+    g = torch.Generator().manual_seed(5)
+    steps = LAYERS * T
+    q = torch.randn(steps, B, NH, dqk, generator=g).bfloat16()
+    k = torch.randn(steps, B, NH, dqk, generator=g).bfloat16()
+    v = torch.randn(steps, B, NH, dv, generator=g).bfloat16()
+    i = torch.randn(steps, B, NH, generator=g).bfloat16()
+    f = (torch.randn(steps, B, NH, generator=g) + 3).bfloat16()
+
+    def fresh_states():
+        gs = torch.Generator().manual_seed(6)
+        return [[(torch.randn(B, NH, dqk, dv, generator=gs).cuda() * 0.1, torch.randn(B, NH, dqk, generator=gs).cuda() * 0.1,
+                  torch.zeros(B, NH, device="cuda")),
+                 tuple(torch.empty(s, device="cuda") for s in ((B, NH, dqk, dv), (B, NH, dqk), (B, NH)))] for _ in range(LAYERS)]
+
+    # reference: the plain op, layer by layer
+    st = [s[0] for s in fresh_states()]
+    h_ref = []
+    for t in range(steps):
+        l = t % LAYERS
+        h, st[l] = ops.mlstm_step(q[t].cuda(), k[t].cuda(), v[t].cuda(), i[t].cuda(), f[t].cuda(), st[l])
+        h_ref.append(h)
+
+    for captured in (False, True):
+        pipe = DecodePipeline(B, NH, dqk, dv, "cuda", group=group)
+        packed = [pipe.pack(q[t], k[t], v[t], i[t], f[t]) for t in range(steps)]
+        h_host = [torch.empty(B, NH, dv, dtype=torch.bfloat16).pin_memory() for _ in range(steps)]
+        states = fresh_states()
+        side = [0] * LAYERS
+        items = []
+        for t in range(steps):
+            l = t % LAYERS
+            items.append((packed[t], states[l][side[l]], states[l][side[l] ^ 1], h_host[t], True))
+            side[l] ^= 1
+        if captured:
+            graph = pipe.capture(items)
+            graph.replay()
+            torch.cuda.synchronize()
+        else:
+            for lo in range(0, steps, group):
+                pipe.step_group(items[lo:lo + group])
+            pipe.synchronize()
+        for t in range(steps):
+            assert torch.equal(h_host[t], h_ref[t].cpu()), (captured, t)
+        for l in range(LAYERS):
+            for got, want in zip(states[l][side[l]], st[l]):
+                assert torch.equal(got, want)
+
+
 # ---- chunkwise -------------------------------------------------------------------
 def test_chunkwise_config1_fp32(ops, golden):
     g = golden("mlstm_c1_fp32")
