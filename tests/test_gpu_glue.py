@@ -139,7 +139,8 @@ def test_swiglu_golden(ops, golden):
     np.testing.assert_allclose(host(y), g["sw_y"], rtol=1e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 10944), (4, 64), (3, 41), (257, 2048)])
+@pytest.mark.parametrize("rows,cols", [(1, 10944), (4, 64), (3, 41), (257, 2048),
+                                       (4100, 10944), (40000, 1000)])   # the last two: the streamed kernel
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_swiglu_dense_and_column_blocks(ops, rows, cols, dtype):
     rng = np.random.default_rng(rows + cols)

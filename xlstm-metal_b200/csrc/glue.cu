@@ -218,12 +218,13 @@ __global__ void __launch_bounds__(RW_WARPS * 32) rms_norm_warp_kernel(const T *_
     }
 }
 
-// Residual add + RMSNorm over many rows, as a stream: one warp per row, 8 warps per CTA, one CTA per SM.  The two
-// input rows (x and the residual) arrive through a ring of RS_RING chunks per warp in shared memory, a chunk being
-// one 16-byte vector of x and one of r per lane (1 KB per warp), filled by cp.async RS_RING chunks ahead - across
-// row boundaries - so 192 KB per SM are in flight whatever the registers do.  The sum s = x + r is rounded to the
+// Residual add + RMSNorm over many rows, as a stream: one warp per row, 16 warps per CTA, one CTA per SM (with 8
+// warps the kernel was bound by instruction issue: two warps per scheduler cannot hide their own dependent
+// instructions).  The two input rows (x and the residual) arrive through a ring of RS_RING chunks per warp in
+// shared memory, a chunk being one 16-byte vector of x and one of r per lane (1 KB per warp), filled by cp.async
+// RS_RING chunks ahead - across row boundaries - so 192 KB per SM are in flight whatever the registers do.  The sum s = x + r is rounded to the
 // activation type, stored as the new residual stream and kept packed in registers for the second pass.
-constexpr int RS_WARPS = 8, RS_RING = 24;
+constexpr int RS_WARPS = 16, RS_RING = 12;
 
 template <typename T, int NV>
 __global__ void __launch_bounds__(RS_WARPS * 32, 1) add_rms_norm_stream_kernel(const T *__restrict__ x, const T *__restrict__ r,
@@ -458,6 +459,114 @@ __global__ void __launch_bounds__(OG_WARPS * 32) mlstm_output_gate_kernel(
     }
 }
 
+// The same epilogue over MANY rows, as a stream (the form of add_rms_norm_stream_kernel): 16 warps per CTA, one
+// CTA per SM, a warp per row; the h row and the gate row arrive through a ring of OGS_RING chunks per warp in
+// shared memory (a chunk = one 16-byte vector of h and one of the gate per lane), filled by cp.async OGS_RING
+// chunks ahead across row boundaries, so the bytes in flight do not depend on the register allocation.  With
+// rows in registers the kernel sat at 16 resident warps per SM and 64 KB in flight: 0.73 of the copy peak.
+constexpr int OGS_WARPS = 16, OGS_RING = 12;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(OGS_WARPS * 32, 1) mlstm_output_gate_stream_kernel(
+    const T *__restrict__ h, const T *__restrict__ og, const T *__restrict__ w, T *__restrict__ y, int64_t rows, int NH,
+    int S, int dv, int64_t hsb, int64_t hsh, int64_t hss, int64_t ldo, float eps) {
+    constexpr int VN = Vec16<T>::N;
+    constexpr int NT = OGS_WARPS * 32;
+    extern __shared__ __align__(16) unsigned char ogs_smem[];
+    uint4 *ring = reinterpret_cast<uint4 *>(ogs_smem);         // [OGS_RING][2][NT]
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int nvec = dv / VN;
+    const int64_t stride = (int64_t)gridDim.x * OGS_WARPS;     // a multiple of NH: the warp stays on one head
+    const int64_t row0 = (int64_t)blockIdx.x * OGS_WARPS + (tid >> 5);
+    if (row0 >= rows) return;                                   // no CTA barrier below
+    const int my_rows = (int)((rows - row0 + stride - 1) / stride);
+    const int head = (int)(row0 % NH);
+    const int64_t bs_step = stride / NH, b_step = bs_step / S;
+    const int s_step = (int)(bs_step % S);
+    const T *hbase = h + head * hsh;
+    const T *ogbase = og + (size_t)head * dv;
+    // the copy stream: position (a_b, a_s, a_bs) of the row it is in, a_i the chunk of that row it issues next
+    int a_k = 0, a_i = 0;
+    int64_t a_bs = row0 / NH, a_b = a_bs / S;
+    int a_s = (int)(a_bs % S);
+    auto issue = [&](int slot) {
+        if (a_k < my_rows) {
+            const int iv = lane + 32 * a_i;
+            if (iv < nvec) {
+                cp_async16(ring + (size_t)(slot * 2 + 0) * NT + tid, hbase + a_b * hsb + a_s * hss + (size_t)iv * VN);
+                cp_async16(ring + (size_t)(slot * 2 + 1) * NT + tid, ogbase + a_bs * ldo + (size_t)iv * VN);
+            }
+            if (++a_i == NV) {
+                a_i = 0;
+                ++a_k;
+                a_bs += bs_step;
+                a_b += b_step;
+                a_s += s_step;
+                if (a_s >= S) {
+                    a_s -= S;
+                    ++a_b;
+                }
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll 1
+    for (int c = 0; c < OGS_RING; ++c) issue(c);
+    // the norm weight of the head, packed
+    uint4 wv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (w && lane + 32 * i < nvec) wv[i] = ldg16_raw(w + (size_t)head * dv + (size_t)(lane + 32 * i) * VN);
+    int slot = 0;
+    for (int k = 0; k < my_rows; ++k) {
+        T *yr = y + (row0 + (int64_t)k * stride) * dv;
+        uint4 hv[NV], ov[NV];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            cp_async_wait<OGS_RING - 1>();                      // the oldest chunk in flight has landed
+            if (lane + 32 * i < nvec) {
+                hv[i] = ring[(size_t)(slot * 2 + 0) * NT + tid];
+                ov[i] = ring[(size_t)(slot * 2 + 1) * NT + tid];
+                float v[VN];
+                unpack16<T>(hv[i], v);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) ss = fmaf(v[e], v[e], ss);
+            }
+            issue(slot);                                        // refill the slot just consumed
+            slot = slot + 1 == OGS_RING ? 0 : slot + 1;
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int iv = lane + 32 * i;
+            if (iv < nvec) {
+                float v[VN], o[VN], wf[VN];
+                unpack16<T>(hv[i], v);
+                unpack16<T>(ov[i], o);
+                if (w) unpack16<T>(wv[i], wf);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) v[e] = v[e] * inv * (w ? wf[e] : 1.0f) * og_sigmoid<T>(o[e]);
+                st16<T>(yr + (size_t)iv * VN, v);
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <typename T, int NV>
+static int output_gate_stream_launch(const T *hp, const T *op, const T *wp, T *yp, int64_t rows, int NH, int S, int dv,
+                                     const int64_t *hs, int64_t ldo, float eps, cudaStream_t st) {
+    auto kern = mlstm_output_gate_stream_kernel<T, NV>;
+    const size_t smem = (size_t)OGS_RING * 2 * OGS_WARPS * 32 * sizeof(uint4);
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return XLSTM_ERR_CUDA;
+    int grid = 148;
+    while ((grid * OGS_WARPS) % NH) ++grid;                     // row stride of the grid: a multiple of NH
+    kern<<<grid, OGS_WARPS * 32, smem, st>>>(hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
+    return launch_status();
+}
+
 template <typename T>
 static int output_gate_launch(const void *h, const void *og, const void *w, void *y, int B, int NH, int S, int dv,
                               const int64_t *hs, int64_t ldo, float eps, cudaStream_t st) {
@@ -472,6 +581,15 @@ static int output_gate_launch(const void *h, const void *og, const void *w, void
     const unsigned grid = (unsigned)(want < cap ? want : cap);
     const T *hp = static_cast<const T *>(h), *op = static_cast<const T *>(og), *wp = static_cast<const T *>(w);
     T *yp = static_cast<T *>(y);
+    // many rows (prefill): the streamed kernel; 16-byte copies need 16-byte aligned rows
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(og)) & 15u) == 0 &&
+                           (hs[0] * sizeof(T)) % 16 == 0 && (hs[1] * sizeof(T)) % 16 == 0 && (hs[2] * sizeof(T)) % 16 == 0 &&
+                           (ldo * sizeof(T)) % 16 == 0 && dv % VN == 0;
+    if (aligned16 && rows >= 4 * 148 * OGS_WARPS && NH <= 64) {
+        if (nvec <= 32) return output_gate_stream_launch<T, 1>(hp, op, wp, yp, rows, NH, S, dv, hs, ldo, eps, st);
+        if (nvec <= 64) return output_gate_stream_launch<T, 2>(hp, op, wp, yp, rows, NH, S, dv, hs, ldo, eps, st);
+        if (nvec <= 128) return output_gate_stream_launch<T, 4>(hp, op, wp, yp, rows, NH, S, dv, hs, ldo, eps, st);
+    }
     const dim3 g(grid), blk(OG_WARPS * 32);
     if (nvec <= 32) return launch_overlapped(mlstm_output_gate_kernel<T, 1>, g, blk, 0, st, hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
     if (nvec <= 64) return launch_overlapped(mlstm_output_gate_kernel<T, 2>, g, blk, 0, st, hp, op, wp, yp, rows, NH, S, dv, hs[0], hs[1], hs[2], ldo, eps);
@@ -514,6 +632,75 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T *__restrict__ g, co
     }
 }
 
+// Many rows: the same gate as a stream.  The 512-byte chunks (one 16-byte vector of g and of u per lane) of all rows
+// form one sequence, dealt to the warps of the grid round-robin (neighbouring warps read neighbouring chunks);
+// a warp's chunks arrive through its ring in shared memory, SGS_RING chunks ahead, by cp.async.
+constexpr int SGS_WARPS = 16, SGS_RING = 12;
+
+template <typename T> __device__ __forceinline__ float silu_stream(float x) {
+    if (sizeof(T) == 2) {   // bf16 result: the sigmoid from one tanh.approx (relative error 2^-11)
+        float t;
+        const float hx = 0.5f * x;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(hx));
+        return fmaf(hx, t, hx);
+    }
+    return x / (1.0f + expf(-x));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SGS_WARPS * 32, 1) swiglu_stream_kernel(const T *__restrict__ g, const T *__restrict__ u,
+                                                                         T *__restrict__ y, int rows, int cols, int64_t ldg,
+                                                                         int64_t ldu) {
+    constexpr int VN = Vec16<T>::N;
+    constexpr int NT = SGS_WARPS * 32;
+    extern __shared__ __align__(16) unsigned char sgs_smem[];
+    uint4 *ring = reinterpret_cast<uint4 *>(sgs_smem);         // [SGS_RING][2][NT]
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int nvec = cols / VN, cpr = (nvec + 31) >> 5;          // chunks per row
+    const int gw = blockIdx.x * SGS_WARPS + (tid >> 5), GW = gridDim.x * SGS_WARPS;
+    const int step_row = GW / cpr, step_i = GW % cpr;            // a warp's next chunk: GW chunks further on
+    // position of the chunk the copy stream issues next, and of the chunk the compute loop consumes next
+    int a_row = gw / cpr, a_i = gw % cpr, c_row = a_row, c_i = a_i;
+    auto advance = [&](int &row, int &i) {
+        row += step_row;
+        i += step_i;
+        if (i >= cpr) {
+            i -= cpr;
+            ++row;
+        }
+    };
+    auto issue = [&](int slot) {
+        if (a_row < rows) {
+            const int iv = lane + 32 * a_i;
+            if (iv < nvec) {
+                cp_async16(ring + (size_t)(slot * 2 + 0) * NT + tid, g + (size_t)a_row * ldg + (size_t)iv * VN);
+                cp_async16(ring + (size_t)(slot * 2 + 1) * NT + tid, u + (size_t)a_row * ldu + (size_t)iv * VN);
+            }
+            advance(a_row, a_i);
+        }
+        cp_async_commit();
+    };
+#pragma unroll 1
+    for (int c = 0; c < SGS_RING; ++c) issue(c);
+    int slot = 0;
+    while (c_row < rows) {
+        cp_async_wait<SGS_RING - 1>();                          // the oldest chunk in flight has landed
+        const int iv = lane + 32 * c_i;
+        if (iv < nvec) {
+            float a[VN], b[VN];
+            unpack16<T>(ring[(size_t)(slot * 2 + 0) * NT + tid], a);
+            unpack16<T>(ring[(size_t)(slot * 2 + 1) * NT + tid], b);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) a[e] = silu_stream<T>(a[e]) * b[e];
+            st16<T>(y + (size_t)c_row * cols + (size_t)iv * VN, a);
+        }
+        advance(c_row, c_i);
+        issue(slot);                                            // refill the slot just consumed
+        slot = slot + 1 == SGS_RING ? 0 : slot + 1;
+    }
+    cp_async_wait<0>();
+}
+
 template <typename T>
 __global__ void swiglu_scalar_kernel(const T *__restrict__ g, const T *__restrict__ u, T *__restrict__ y, int64_t rows,
                                      int cols, int64_t ldg, int64_t ldu) {
@@ -533,7 +720,12 @@ static int swiglu_launch(const void *g, const void *u, void *y, int64_t rows, in
     const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0 &&
                          cols % VN == 0 && ldg % VN == 0 && ldu % VN == 0;
     const T *gp = static_cast<const T *>(g), *up = static_cast<const T *>(u);
-    if (aligned) {
+    if (aligned && rows * (int64_t)((cols / VN + 31) / 32) >= 64 * 148 * SGS_WARPS && rows < (1 << 24) && cols < (1 << 24)) {
+        auto kern = swiglu_stream_kernel<T>;
+        const size_t smem = (size_t)SGS_RING * 2 * SGS_WARPS * 32 * sizeof(uint4);
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return XLSTM_ERR_CUDA;
+        kern<<<148, SGS_WARPS * 32, smem, st>>>(gp, up, static_cast<T *>(y), (int)rows, cols, ldg, ldu);
+    } else if (aligned) {
         const unsigned grid = (unsigned)(rows < 148 * 8 ? rows : 148 * 8);   // 8 resident CTAs per SM
         swiglu_kernel<T><<<grid, 256, 0, st>>>(gp, up, static_cast<T *>(y), rows, cols, ldg, ldu);
     } else {
