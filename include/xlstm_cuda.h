@@ -260,6 +260,25 @@ int xlstm_mlstm_step_ex(const void *q, const void *k, const void *v, const void 
                         void *h, float *C1, float *n1, float *m1,
                         int B, int NH, int dqk, int dv, float eps, float gate_cap, int flags, int dtype,
                         void *stream);
+/*
+ * Decode step WITH the layer's output epilogue applied before the result leaves the chip (single token):
+ *   y[b, head*dv + j] = h_j / sqrt(mean_j(h^2) + norm_eps) * norm_w[head*dv + j] * sigmoid(ogate[b, head*dv + j])
+ * where h is what xlstm_mlstm_step_ex would have written (rounded to the activation type first, as the separate
+ * epilogue reads it back).  The CTAs that hold the dv / 64 column tiles of one head run as one thread-block
+ * cluster and exchange their partial sums of squares through distributed shared memory, so h itself is never
+ * stored.  ogate: rows of pitch ogate_ld elements (a column block of the fused projection output), norm_w:
+ * [NH*dv] or NULL, y: [B, NH*dv] dense.  dv <= 512 (eight tiles: the portable cluster size), else
+ * XLSTM_ERR_UNSUPPORTED.  flags, gate_cap as in xlstm_mlstm_step_ex.
+ * Replaces mLSTMRecurrentKernelCell.forward at S = 1 followed by mLSTMOutputCell.forward's per-head norm,
+ * sigmoid and product (mlstm_recurrent_kernel_cell.py:106-153, mlstm_output_cell.py:84-94,
+ * multihead_norm.py:43-64).
+ */
+int xlstm_mlstm_step_gated(const void *q, const void *k, const void *v, const void *ig, const void *fg,
+                           const float *C0, const float *n0, const float *m0,
+                           const void *ogate, int64_t ogate_ld, const void *norm_w, float norm_eps,
+                           void *y, float *C1, float *n1, float *m1,
+                           int B, int NH, int dqk, int dv, float eps, float gate_cap, int flags, int dtype,
+                           void *stream);
 int xlstm_mlstm_chunkwise_fwd_gatecap(const void *q, const void *k, const void *v, const void *ig, const void *fg,
                                       const float *C0, const float *n0, const float *m0,
                                       void *h, float *C1, float *n1, float *m1,

@@ -246,6 +246,39 @@ def test_decode_pipeline_host_fed(ops, group):
                 assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("B,NH,dqk,dv", [(2, 4, 128, 256), (1, 8, 256, 512), (3, 2, 64, 96)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mlstm_step_with_fused_output_epilogue(ops, B, NH, dqk, dv, dtype):
+    """xlstm_mlstm_step_gated (norm x weight x sigmoid(output gate) applied inside the step kernel, the head's
+    CTAs meeting through their cluster) against the two separate kernels and against the oracle; the output gate
+    is handed over as a column block of a wider projection output, as the block does."""
+    rng = np.random.default_rng(B * 100 + dv)
+    rnd = (lambda a: xo.bf16_round(a)) if dtype == torch.bfloat16 else (lambda a: a)
+    q, k = (rnd(rng.standard_normal((B, NH, dqk)).astype(np.float32)) for _ in range(2))
+    v = rnd(rng.standard_normal((B, NH, dv)).astype(np.float32))
+    i, f = (rnd(a[:, :, 0]) for a in gates(rng, (B, NH, 1)))
+    wide = rnd(rng.standard_normal((B, NH * dv + 24)).astype(np.float32) * 2.0)
+    og = wide[:, 16:16 + NH * dv]
+    w = rnd(rng.uniform(0.5, 1.5, NH * dv).astype(np.float32))
+    st = (rng.standard_normal((B, NH, dqk, dv)).astype(np.float32) * 0.1,
+          rng.standard_normal((B, NH, dqk)).astype(np.float32) * 0.1, rng.standard_normal((B, NH)).astype(np.float32))
+    d = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dtype).cuda()
+    wide_d = d(wide)
+    for state in (st, None):
+        sd = None if state is None else tuple(dev(x) for x in state)
+        h, st_ref = ops.mlstm_step(d(q), d(k), d(v), d(i), d(f), sd)
+        y_ref = ops.mlstm_output_gate(h.unsqueeze(2), wide_d[:, 16:16 + NH * dv].unsqueeze(1), d(w), 1e-6)[:, 0]
+        y, st_new = ops.mlstm_step_gated(d(q), d(k), d(v), d(i), d(f), wide_d[:, 16:16 + NH * dv], d(w), sd, norm_eps=1e-6)
+        tol = FP32_TOL if dtype == torch.float32 else BF16_TOL
+        assert y.shape == (B, NH * dv) and relerr(host(y), host(y_ref)) <= tol
+        for got, want in zip(st_new, st_ref):
+            assert torch.equal(got, want)
+        # and against the oracle: recurrent step, then the epilogue restated on the host
+        h_o, _ = xo.mlstm_recurrent(q[:, :, None], k[:, :, None], v[:, :, None], i[:, :, None], f[:, :, None], state)
+        y_o = xo.mlstm_output_gate(rnd(h_o), og[:, None, :], w, 1e-6)[:, 0]
+        assert relerr(host(y), y_o) <= tol * (1 if dtype == torch.float32 else 2)
+
+
 # ---- chunkwise -------------------------------------------------------------------
 def test_chunkwise_config1_fp32(ops, golden):
     g = golden("mlstm_c1_fp32")

@@ -43,6 +43,16 @@ __device__ __forceinline__ void st4(__nv_bfloat16 *p, float4 v) {
 // fp32 rounding on the soft-capped range |x| <= 15 and finite everywhere.
 __device__ __forceinline__ float logsigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+// sigmoid of an output-gate pre-activation: bf16 outputs take it from ONE special-function op (tanh.approx, relative
+// error 2^-11, below the bf16 rounding), fp32 outputs the exact form
+template <typename T> __device__ __forceinline__ float gate_sigmoid(float x) {
+    if (sizeof(T) == 2) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+        return fmaf(0.5f, t, 0.5f);
+    }
+    return 1.0f / (1.0f + expf(-x));
+}
 // gate soft-cap folded into the kernels that consume the gates: cap <= 0 leaves x as it is
 __device__ __forceinline__ float gate_softcap(float x, float cap) { return cap > 0.0f ? cap * tanhf(x / cap) : x; }
 

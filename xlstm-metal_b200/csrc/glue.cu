@@ -352,16 +352,7 @@ constexpr int OG_WARPS = 8;
 
 __device__ __forceinline__ uint4 ldg16_raw(const void *p) { return *reinterpret_cast<const uint4 *>(p); }
 
-// sigmoid for the output gate: bf16 outputs take it from ONE special-function op (tanh.approx, relative error
-// 2^-11, below the bf16 rounding), fp32 outputs the exact form
-template <typename T> __device__ __forceinline__ float og_sigmoid(float x) {
-    if (sizeof(T) == 2) {
-        float t;
-        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
-        return fmaf(0.5f, t, 0.5f);
-    }
-    return 1.0f / (1.0f + expf(-x));
-}
+template <typename T> __device__ __forceinline__ float og_sigmoid(float x) { return gate_sigmoid<T>(x); }
 
 // The warps of the grid walk the rows; a warp holds its row (h and the gate pre-activations) as packed 16-byte
 // vectors and has the NEXT row's loads in flight while it reduces, scales and stores the current one.  The row

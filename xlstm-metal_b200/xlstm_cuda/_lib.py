@@ -40,6 +40,8 @@ _SIGNATURES = {
                                  + [c_float, c_float, c_int, c_void_p]),
     "xlstm_mlstm_step_ex": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 4
                             + [c_float, c_float, c_int, c_int, c_void_p]),
+    "xlstm_mlstm_step_gated": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p, c_int64, c_void_p, c_float]
+                               + [c_void_p] * 4 + [c_int] * 4 + [c_float, c_float, c_int, c_int, c_void_p]),
     "xlstm_mlstm_chunkwise_fwd_gatecap": (c_int, [c_void_p] * 5 + [c_void_p] * 3 + [c_void_p] * 4 + [c_int] * 6
                                           + [c_float, c_float, c_int, ctypes.POINTER(c_int64), c_void_p, c_size_t, c_void_p]),
     "xlstm_rms_norm": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_float, c_int, c_void_p]),

@@ -352,8 +352,8 @@ class mLSTMBlock(nn.Module):
 
     def _token_step(self, x: torch.Tensor, state: Optional[State]):
         """Single-token path (at most 4 sequences, bf16, fused weights): every Linear is one
-        weight-streaming kernel with its norm / bias / residual / SwiGLU folded in, so a block is six
-        launches: projections, cell step, output epilogue, out-projection, FFN up, FFN down."""
+        weight-streaming kernel with its norm / bias / residual / SwiGLU folded in, so a block is five
+        launches: projections, cell step with the output epilogue, out-projection, FFN up, FFN down."""
         cell = self.mlstm_cell
         W, b = cell._fused_weights()
         B = x.shape[0]
@@ -363,11 +363,18 @@ class mLSTMBlock(nn.Module):
         o_k, o_v, o_g, o_o = NH * dqk, 2 * NH * dqk, 2 * NH * dqk + NH * dv, 2 * NH * dqk + NH * dv + 2 * NH
         q, k, v = y[:, :o_k].view(B, NH, dqk), y[:, o_k:o_v].view(B, NH, dqk), y[:, o_v:o_g].view(B, NH, dv)
         rk = cell.recurrent_kernel
-        h, new_state = ops.mlstm_step(q, k, v, y[:, o_g:o_g + NH], y[:, o_g + NH:o_o], state, rk.eps,
-                                      inplace=rk.inplace_state, gate_cap=cell.projection_cell.gate_soft_cap,
-                                      state_settled=True)   # the launch before this one is the projection above
         oc = cell.output_cell
-        gated = ops.mlstm_output_gate(h.unsqueeze(2), y[:, o_o:].unsqueeze(1), oc.norm.weight, oc.norm.eps)
+        if dv <= 512 and dv % 4 == 0:
+            # cell step and output epilogue in one launch: the head's column-tile CTAs meet through their cluster
+            gated, new_state = ops.mlstm_step_gated(
+                q, k, v, y[:, o_g:o_g + NH], y[:, o_g + NH:o_o], y[:, o_o:], oc.norm.weight, state, rk.eps, oc.norm.eps,
+                inplace=rk.inplace_state, gate_cap=cell.projection_cell.gate_soft_cap,
+                state_settled=True)   # the launch before this one is the projection above
+        else:
+            h, new_state = ops.mlstm_step(q, k, v, y[:, o_g:o_g + NH], y[:, o_g + NH:o_o], state, rk.eps,
+                                          inplace=rk.inplace_state, gate_cap=cell.projection_cell.gate_soft_cap,
+                                          state_settled=True)
+            gated = ops.mlstm_output_gate(h.unsqueeze(2), y[:, o_o:].unsqueeze(1), oc.norm.weight, oc.norm.eps)
         x1 = ops.linear_token(oc.out_proj.weight, gated.reshape(B, -1), bias=oc.out_proj.bias, residual=x2)
         act = ops.linear_token(self._fused_ffn(), x1, norm_weight=self.norm_ffn.weight, norm_eps=self.norm_ffn.eps,
                                swiglu_pair=True)

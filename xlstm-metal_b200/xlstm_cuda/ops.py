@@ -87,6 +87,43 @@ def mlstm_step(q, k, v, i, f, state=None, eps: float = 1e-6, inplace: bool = Fal
     return h, (C1, n1, m1)
 
 
+def mlstm_step_gated(q, k, v, i, f, ogate, norm_weight, state=None, eps: float = 1e-6, norm_eps: float = 1e-6,
+                     inplace: bool = False, gate_cap: Optional[float] = None, state_settled: bool = False):
+    """Decode step with the output epilogue fused in: returns ``y [B, NH*dv] = MultiHeadRMSNorm(h) * weight *
+    sigmoid(ogate)`` and the new state; ``h`` itself is never written.  ``ogate: [B, NH*dv]``, possibly a column
+    block of a wider one-row-per-sequence tensor (row stride >= NH*dv).  ``dv`` must be at most 512."""
+    _need_cuda(q, k, v, i, f, ogate, norm_weight)
+    B, NH, dqk = q.shape
+    dv = v.shape[-1]
+    dt = _dtype_code(q)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    i, f = i.to(q.dtype).contiguous(), f.to(q.dtype).contiguous()
+    og = ogate.to(q.dtype)
+    if og.dim() != 2 or og.stride(1) != 1 or og.shape[1] != NH * dv:
+        og = og.reshape(B, NH * dv).contiguous()
+    ld = og.stride(0) if B > 1 else NH * dv
+    if ld < NH * dv:
+        og, ld = og.contiguous(), NH * dv
+    w = None if norm_weight is None else norm_weight.to(q.dtype).contiguous()
+    if state is not None:
+        C0, n0, m0 = (_state32(s) for s in state)
+        m0 = m0.reshape(B, NH)
+    else:
+        C0 = n0 = m0 = None
+    dev = q.device
+    y = torch.empty(B, NH * dv, dtype=q.dtype, device=dev)
+    C1 = C0 if (inplace and C0 is not None) else torch.empty(B, NH, dqk, dv, dtype=torch.float32, device=dev)
+    n1 = torch.empty(B, NH, dqk, dtype=torch.float32, device=dev)
+    m1 = torch.empty(B, NH, dtype=torch.float32, device=dev)
+    flags = _lib.STEP_STATE_SETTLED if (state_settled and state is not None) else 0
+    _lib.check(_lib.load().xlstm_mlstm_step_gated(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), i.data_ptr(), f.data_ptr(), _ptr(C0), _ptr(n0), _ptr(m0),
+        og.data_ptr(), int(ld), _ptr(w), float(norm_eps), y.data_ptr(), C1.data_ptr(), n1.data_ptr(), m1.data_ptr(),
+        B, NH, dqk, dv, float(eps), float(gate_cap) if gate_cap is not None else 0.0, flags, dt, _stream()),
+        "xlstm_mlstm_step_gated")
+    return y, (C1, n1, m1)
+
+
 def _strides3(t: torch.Tensor):
     # [B,NH,S,d] view with a contiguous last dimension -> (batch, head, token) element strides
     return [t.stride(0), t.stride(1), t.stride(2)]
