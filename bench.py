@@ -19,7 +19,7 @@ At N > 1 the decode batch is sharded (global batch 16*N, no collective): weak sc
 under oracle/_ref by oracle/make_ref.py) on all host cores for the same workload at the same global
 batch; where that file is absent it times the C restatement (oracle/, OpenMP over batch x heads).
 The JSON line stays short: the prefill / sLSTM / soft-cap figures ride inside ``roofline``; the long
-per-kernel tables (glue kernels, 7B-shaped model) go to ``gpurun_out/bench_details.json``.
+per-kernel tables (glue kernels, 7B-shaped model) go to ``bench_details_n{N}.json`` in the run's output folder.
 """
 from __future__ import annotations
 

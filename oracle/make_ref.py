@@ -11,6 +11,7 @@ the checkout is absent the recipe does nothing and the arm falls back to the C r
 from __future__ import annotations
 
 import importlib.util
+import os
 import shutil
 from pathlib import Path
 
@@ -20,9 +21,11 @@ CELL_REL = "xlstm_metal/torch_native/blocks/mlstm/mlstm_chunkwise/mlstm_recurren
 CELL_FILE = REF_DIR / "mlstm_recurrent_kernel_cell.py"
 
 
-def build(reference_root: str = "/root/reference") -> Path | None:
-    """Copy the cell file if the reference checkout is present; return its path (or None)."""
-    src = Path(reference_root) / CELL_REL
+def build(reference_root: str | None = None) -> Path | None:
+    """Copy the cell file if the reference checkout is present; return its path (or None).  The checkout is looked
+    for at ``reference_root``, else at ``$XLSTM_REFERENCE_ROOT``, else in a ``reference`` folder beside the repository."""
+    root = reference_root or os.environ.get("XLSTM_REFERENCE_ROOT") or str(_HERE.parent.parent / "reference")
+    src = Path(root) / CELL_REL
     if src.exists():
         REF_DIR.mkdir(parents=True, exist_ok=True)
         if not CELL_FILE.exists() or CELL_FILE.read_bytes() != src.read_bytes():
