@@ -182,6 +182,7 @@ mlstm_gate_chain_kernel(const float *__restrict__ m0, double *__restrict__ chain
 // so one cheap pass over the P local states yields the true state at the start of every segment (Cs, ns, ms)
 // and the final state.  One CTA per (head, slab of elements); the scalar chain is recomputed per CTA.
 constexpr int COMB_THREADS = 256;
+constexpr int COMB_VEC = 4;        // elements per thread (one 16-byte vector)
 __global__ void __launch_bounds__(COMB_THREADS)
 mlstm_segment_combine_kernel(const float *__restrict__ C0, const float *__restrict__ n0, const float *__restrict__ m0,
                              const float *__restrict__ Cl, const float *__restrict__ nl, const float *__restrict__ ml,
@@ -189,36 +190,60 @@ mlstm_segment_combine_kernel(const float *__restrict__ C0, const float *__restri
                              float *__restrict__ ms, float *__restrict__ C1, float *__restrict__ n1, float *__restrict__ m1,
                              int NCH, int P, int seg_tiles, int dqk, int dv) {
     __shared__ float s_wc[64], s_wl[64];   // weights of the carried and of the local state per segment (P <= 64)
+    __shared__ double s_G[64];             // summed log forget gates per segment
     const int bh = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // per-segment sums by the warps (lanes stride over the segment's tiles), then one thread chains the P segments
+    for (int j = warp; j < P; j += COMB_THREADS / 32) {
+        const int tile0 = j * seg_tiles, n = min(seg_tiles, NCH - tile0);
+        double G = 0.0;
+        for (int c = lane; c < n; c += 32) G += chain[((size_t)bh * NCH + tile0 + c) * GC + 0];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) G += __shfl_xor_sync(0xffffffffu, G, o);
+        if (lane == 0) s_G[j] = G;
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         double m = C0 ? (double)m0[bh] : 0.0;
         for (int j = 0; j < P; ++j) {
-            const int tile0 = j * seg_tiles, n = min(seg_tiles, NCH - tile0);
-            double G = 0.0;
-            for (int c = 0; c < n; ++c) G += chain[((size_t)bh * NCH + tile0 + c) * GC + 0];
             const double mloc = (double)ml[(size_t)bh * P + j];
-            const double mn = fmax(G + m, mloc);
+            const double mn = fmax(s_G[j] + m, mloc);
             if (blockIdx.y == 0) ms[(size_t)bh * P + j] = (float)m;
-            s_wc[j] = (float)exp(G + m - mn);
+            s_wc[j] = (float)exp(s_G[j] + m - mn);
             s_wl[j] = (float)exp(mloc - mn);
             m = mn;
         }
         if (blockIdx.y == 0) m1[bh] = (float)m;
     }
     __syncthreads();
-    const size_t CE = (size_t)dqk * dv, total = CE + dqk;   // elements of C, then of n
-    for (size_t e = (size_t)blockIdx.y * COMB_THREADS + threadIdx.x; e < total; e += (size_t)gridDim.y * COMB_THREADS) {
+    // elements of C, then of n, as 16-byte vectors (dqk * dv and dqk are multiples of 4); a thread owns one vector
+    // of every segment: its P loads are independent of the chain and are issued ahead of it, 8 at a time
+    const size_t CE = (size_t)dqk * dv, total_vec = (CE + dqk) / COMB_VEC;
+    for (size_t e4 = (size_t)blockIdx.y * COMB_THREADS + threadIdx.x; e4 < total_vec; e4 += (size_t)gridDim.y * COMB_THREADS) {
+        const size_t e = e4 * COMB_VEC;
         const bool isC = e < CE;
         const size_t off = isC ? e : e - CE, per = isC ? CE : (size_t)dqk;
         const float *src0 = isC ? C0 : n0, *loc = isC ? Cl : nl;
         float *st = isC ? Cs : ns, *fin = isC ? C1 : n1;
-        float v = C0 ? src0[(size_t)bh * per + off] : 0.f;
-        for (int j = 0; j < P; ++j) {
-            const size_t idx = ((size_t)bh * P + j) * per + off;
-            st[idx] = v;
-            v = s_wc[j] * v + s_wl[j] * loc[idx];
+        float4 v = C0 ? *reinterpret_cast<const float4 *>(src0 + (size_t)bh * per + off) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j0 = 0; j0 < P; j0 += 8) {
+            float4 l[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (j0 + u < P) l[u] = ldg_stream(loc + ((size_t)bh * P + j0 + u) * per + off);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (j0 + u < P) {
+                    const int j = j0 + u;
+                    stg_stream(st + ((size_t)bh * P + j) * per + off, v);
+                    const float wc = s_wc[j], wl = s_wl[j];
+                    v.x = wc * v.x + wl * l[u].x;
+                    v.y = wc * v.y + wl * l[u].y;
+                    v.z = wc * v.z + wl * l[u].z;
+                    v.w = wc * v.w + wl * l[u].w;
+                }
         }
-        fin[(size_t)bh * per + off] = v;
+        *reinterpret_cast<float4 *>(fin + (size_t)bh * per + off) = v;
     }
 }
 
@@ -855,7 +880,7 @@ int mlstm_chunkwise_tc(const ChunkwiseParams &p, void *workspace, size_t workspa
         int rc = forward(nullptr, 1, segA_m, true);
         if (rc != XLSTM_OK) return rc;
         // the true state at the start of every segment, and the final state
-        const int slabs = (int)((CE + p.dqk + 64 * COMB_THREADS - 1) / (64 * COMB_THREADS));
+        const int slabs = (int)(((CE + p.dqk) / COMB_VEC + COMB_THREADS - 1) / COMB_THREADS);   // one vector per thread
         mlstm_segment_combine_kernel<<<dim3(BH, slabs), COMB_THREADS, 0, st>>>(
             p.C0, p.n0, p.C0 ? p.m0 : nullptr, segA_C, segA_n, segA_m, chain, segB_C, segB_n, segB_m, p.C1, n_final,
             m_final, nch, P, seg_tiles, p.dqk, p.dv);
