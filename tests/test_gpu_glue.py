@@ -215,7 +215,8 @@ def test_glue_rejects_cpu_tensors(ops):
 
 
 # ---- single-token Linear (weight-streaming pass with folded norm / residual / SwiGLU) ----------
-@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (1, 12304, 4096), (2, 4096, 10944), (4, 264, 520), (3, 33, 4096)])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (1, 12304, 4096), (2, 4096, 10944), (4, 264, 520), (3, 33, 4096),
+                                   (4, 300, 10944), (1, 500, 16), (2, 1000, 2056)])
 def test_linear_token_plain_bias_residual(ops, M, N, K):
     rng = np.random.default_rng(M * 7 + N + K)
     x = bf(rng.standard_normal((M, K)).astype(np.float32))
