@@ -395,7 +395,7 @@ def run_ours(args):
         r = prefill["roofline"]
         roofline["prefill"] = {
             "frac": r["frac"], "tflops": r["achieved"], "peak_tflops": r["peak"], "hbm_frac": r["hbm_frac"],
-            "cell_ms": prefill["cell_ms"], "tokens_per_s": prefill["cell_tokens_per_s"],
+            "cell_ms": prefill["cell_ms"], "tokens_per_s": prefill["cell_tokens_per_s"], "clocks": prefill["clocks"],
             "with_allgather_outproj_ms": prefill["with_allgather_outproj_ms"],
             "nccl_variant_ms": prefill["nccl_allgather_variant_ms"], "world": world,
             "gather_check": prefill["gather_check"], "gather_gbs_per_rank": prefill["gather_gbs_per_rank"],
@@ -493,11 +493,14 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
         del h_loc, want
         dist.barrier()
     reps = args.prefill_reps
-    e[0].record()
-    for _ in range(reps):
-        h, st = ops.mlstm_chunkwise(q, k, v, i, f, None, L, 1e-6, ws)
-    e[1].record()
-    torch.cuda.synchronize()
+    with ClockSampler(device.index or 0) as pclk:     # the SM clock this kernel runs at under the power cap
+        e[0].record()
+        for _ in range(reps):
+            h, st = ops.mlstm_chunkwise(q, k, v, i, f, None, L, 1e-6, ws)
+        e[1].record()
+        torch.cuda.synchronize()
+    prefill_clocks = {"sm_mhz": (sorted(pclk.samples)[len(pclk.samples) // 2] if pclk.samples else None),
+                      "reasons": sorted(pclk.reasons)}
     if world > 1:
         dist.barrier()
     e[2].record()
@@ -544,7 +547,7 @@ def run_prefill(torch, dist, ops, device, world, rank, args):
     gather_gbs = (world - 1) * Bp * Sp * nh_local * DV * 2 / (cell_ms_gather * 1e-3) / 1e9 if fused is not None else None
     return {"workload": f"mlstm_chunkwise_prefill B={Bp} S={Sp} NH={NH} dqk={DQK} dv={DV} L={L} bf16 (BASELINE configs[3])",
             "parallelism": f"heads sharded x{world}, fused all-gather of h, replicated out-proj", "scaling": "strong",
-            "cell_tokens_per_s": tokens / (cell_ms * 1e-3), "cell_ms": cell_ms,
+            "cell_tokens_per_s": tokens / (cell_ms * 1e-3), "cell_ms": cell_ms, "clocks": prefill_clocks,
             "with_allgather_outproj_tokens_per_s": tokens / (full_ms * 1e-3), "with_allgather_outproj_ms": full_ms,
             "gather": ("fused: kernel epilogue stores h into every rank's buffer over NVLink" if world > 1 else "single rank"),
             "gather_check": gather_check, "gather_gbs_per_rank": gather_gbs, "cell_with_gather_ms": cell_ms_gather,
