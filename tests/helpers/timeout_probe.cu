@@ -1,8 +1,8 @@
-// Test helper (not part of the library): the bounded mbarrier wait of csrc/tcgen05.cuh, built with a tiny
-// poll limit, on a barrier that nobody ever arrives at.  The wait must give up, raise the CTA's abort flag and
+// Test helper (not part of the library): the bounded mbarrier wait of csrc/tcgen05.cuh, built with a small
+// time limit (2^22 SM clocks, ~2 ms), on a barrier that nobody ever arrives at.  The wait must give up, raise the CTA's abort flag and
 // let the kernel end normally - the path the tensor-core kernels take when a device-side wait times out.
 // Nothing here faults, traps or spins without bound.
-#define XL_TC_SPIN_LIMIT 4096u
+#define XL_TC_WAIT_CLOCKS (1ll << 22)
 #include "tcgen05.cuh"
 
 namespace {

@@ -32,15 +32,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// the same with a suspend-time hint: the warp may sleep in hardware for up to `ns` nanoseconds waiting for the
+// phase, instead of coming back to poll (a waiting warp then costs neither issue slots nor energy)
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.b32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 // Bounded wait.  `abort_flag` (shared memory) lets one timed-out role release all others.
-// Returns false on time-out or abort.
-#ifndef XL_TC_SPIN_LIMIT
-#define XL_TC_SPIN_LIMIT (1u << 24)
+// Returns false on time-out or abort.  The warp sleeps in hardware between attempts (20 us at most each); the
+// bound is elapsed SM clocks, about 2 s (a test helper builds this header with a much smaller value).
+#ifndef XL_TC_WAIT_CLOCKS
+#define XL_TC_WAIT_CLOCKS (4ll << 30)
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t it = 0; it < XL_TC_SPIN_LIMIT; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 1023u && *abort_flag) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try_wait_for(bar, parity, 20000u)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > XL_TC_WAIT_CLOCKS) break;
     }
     *abort_flag = 1;
     return false;
