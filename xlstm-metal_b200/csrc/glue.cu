@@ -2,6 +2,9 @@
 // output epilogue (per-head RMS norm x weight x sigmoid(output gate)), the SwiGLU gate and the causal
 // depthwise convolution of the sLSTM projection.  All are single-pass and HBM-bound: every input is
 // read once with 16-byte accesses, reductions and math in fp32, one rounding on the way out.
+// Two forms each: register-resident kernels for few rows (decode), and for many rows (prefill) STREAMED
+// kernels - one CTA of 16 warps per SM, inputs arriving through per-lane rings of 16-byte cp.async slots in
+// shared memory a fixed distance ahead, so the bytes in flight do not depend on the register allocation.
 #include "common.cuh"
 
 namespace xl {

@@ -391,7 +391,7 @@ class mLSTMBlock(nn.Module):
 
     def _token_step_ok(self, x: torch.Tensor) -> bool:
         if getattr(self.mlstm_cell, "_shard", None) is not None:
-            return False   # the six-launch single-token path has no gather step
+            return False   # the single-token launch sequence has no gather step
         return (x.shape[1] == 1 and x.shape[0] <= ops.LINEAR_TOKEN_MAX_ROWS and x.dtype == torch.bfloat16 and
                 self.mlstm_cell._fused_weights() is not None and self._fused_ffn() is not None and
                 self.mlstm_cell.compute_dtype == torch.bfloat16)
