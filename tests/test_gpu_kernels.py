@@ -532,6 +532,13 @@ def test_errors_are_statuses_not_crashes(ops):
     x = torch.zeros(16, device="cuda")
     assert lib.xlstm_softcap(x.data_ptr(), x.data_ptr(), 16, 15.0, 7, None) == -2
     assert lib.xlstm_mlstm_step(*([x.data_ptr()] * 5), None, None, None, *([x.data_ptr()] * 4), 1, 1, 2, 3, 1e-6, 0, None) == -2
+    px = x.data_ptr()
+    # flags the step does not know: invalid; output epilogue wider than eight 64-column tiles: unsupported (no launch)
+    assert lib.xlstm_mlstm_step_ex(*([px] * 5), None, None, None, *([px] * 4), 1, 1, 8, 8, 1e-6, 0.0, 2, 0, None) == -1
+    assert lib.xlstm_mlstm_step_gated(*([px] * 5), None, None, None, px, 1024, None, 1e-6, *([px] * 4), 1, 1, 8, 1024, 1e-6, 0.0,
+                                      0, 0, None) == -2
+    assert lib.xlstm_mlstm_step_gated(*([px] * 5), None, None, None, None, 8, None, 1e-6, *([px] * 4), 1, 1, 8, 8, 1e-6, 0.0,
+                                      0, 0, None) == -1
     with pytest.raises(RuntimeError):
         ops.softcap(torch.zeros(4), 15.0)  # CPU tensor: no fallback
     with pytest.raises(TypeError):

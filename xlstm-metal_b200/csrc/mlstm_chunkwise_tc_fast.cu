@@ -44,7 +44,6 @@ using namespace tcw;
 enum { F_QFULL = 0, F_KFULL, F_VFULL, F_SDONE, F_UPDA, F_UPDB, F_PVDONE, F_VSCALED, F_PREADY, F_CBA, F_CBB,
        F_HFREE, F_QNDONE, F_NDONE, F_HSTAGED, F_VFREE, F_SAREADY, F_NBARS };
 static_assert(F_NBARS <= 24, "barrier slots");
-constexpr int PREFETCH_AHEAD = 2;   // tiles between the L2 prefetch of a box and the iteration that loads it
 
 // C pass for one 128-row half after the state update: optional rescale of C~ in TMEM, then the bf16 copy
 // Cb (in the frame the next tile reads it in); after the last tile the fp32 rows go to `dst` instead.
@@ -203,14 +202,6 @@ __global__ void __launch_bounds__(THREADS, 1) mlstm_chunkwise_tc_fast_kernel(con
             for (int k = 0; k < NCH; ++k) {
                 const int t0 = (tile0 + k) * LT;
                 const uint32_t pp = (k - 1) & 1;
-                // A load that misses L2 takes 2-3 k clocks from issue to completion (DRAM latency, whatever its
-                // size), more than the window in which a single-buffered tile is free: the boxes of the tile after
-                // the next one are pulled into L2 here, a tile and a half before their loads are issued.
-                if (k + PREFETCH_AHEAD < NCH) {
-                    const int tp = (tile0 + k + PREFETCH_AHEAD) * LT;
-                    for (int q = 0; q < NBOX; ++q) { tma_prefetch_4d(&p.tq, q * 64, tp, hd, b); tma_prefetch_4d(&p.tk, q * 64, tp, hd, b); }
-                    for (int q = 0; q < 2; ++q) tma_prefetch_4d(&p.tv, col0 + q * 64, tp, hd, b);
-                }
                 if (k > 0 && !(mbar_wait(&bars[F_SDONE], pp, abort_flag) && mbar_wait(&bars[F_QNDONE], pp, abort_flag))) break;
                 mbar_expect_tx(&bars[F_QFULL], NBOX * SM::BOX);
                 for (int q = 0; q < NBOX; ++q) tma_load_4d(smem + SM::Q + q * SM::BOX, &p.tq, &bars[F_QFULL], q * 64, t0, hd, b);

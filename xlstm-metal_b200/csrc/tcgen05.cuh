@@ -78,12 +78,6 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m
         ::"r"(smem_u32(smem_dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
-// 4-D tile prefetch into L2 (no shared-memory destination, no barrier): the later load of the same box hits L2
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *m, int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
-                 ::"l"(m), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-
 // 4-D tile store shared -> global (bulk async group); the source tile must stay untouched until
 // tma_store_wait_read() returns in the issuing thread.
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, const void *smem_src, int c0, int c1, int c2, int c3) {
