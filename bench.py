@@ -426,10 +426,16 @@ def run_ours(args):
                 details["model"] = mo
                 roofline["model_7b"] = {"prefill_tokens_per_s": mo["prefill_tokens_per_s"],
                                         "decode_tokens_per_s": mo["decode_tokens_per_s"]}
+    if "prefill" in roofline:
+        # the prefill figures close the line (a record that keeps only the end of a long line still has them):
+        # no empty entries, floats to five significant digits
+        pf = {k_: (float(f"{v_:.5g}") if isinstance(v_, float) else v_) for k_, v_ in roofline.pop("prefill").items()
+              if v_ is not None}
+        roofline["prefill"] = pf
     line = {
         "metric": "mlstm_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms_max / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": workload_config(world), "roofline": roofline,
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
         "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / K},
         "gpu_launches": launches, "launch": "CUDA graph replay of the step loop",
@@ -437,6 +443,7 @@ def run_ours(args):
     }
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline() if world == 1 and not args.no_cpu else None
+        line["roofline"] = roofline
         print(json.dumps(line), flush=True)
         try:    # the long per-kernel tables: a file beside the run, not part of the line
             out = ROOT / "gpurun_out"
